@@ -262,6 +262,22 @@ class CacheBlock:
         )
 
 
+def block_page_numbers(block):
+    """Page numbers (``page_start // page_size``) of any block-like object as an int64 array.
+
+    Blocks of this package keep the array between steps (``CacheBlock.page_numbers``); any other
+    object with the reference's public attributes (``page_starts``, ``page_size`` --
+    minisgl/shared_cache/shared_block.py:24-60) is read through those, so the planners also take
+    the reference's own ``CacheBlock``."""
+    cached = getattr(block, "page_numbers", None)
+    if cached is not None:
+        return cached()
+    import numpy as np
+
+    starts = block.page_starts
+    return np.asarray(starts, dtype=np.int64) // int(block.page_size) if len(starts) else np.zeros(0, np.int64)
+
+
 SharedBlock = CacheBlock
 CacheView = List[CacheBlock]
 

@@ -24,28 +24,6 @@
 // value can never reach the accumulator.
 #include "common.cuh"
 
-#ifndef VA_STREAM_PROF
-#define VA_STREAM_PROF 0
-#endif
-#if VA_STREAM_PROF
-// profiling build only: per-warp cycle sums of the streaming kernel's phases
-// [0] total  [1] waits  [2] compute  [3] issue  [4] query staging  [5] partial write  [6] stages  [7] items
-// [8] max end clock  [9] sum of end clocks  [10] warps  [11] min start clock
-__device__ unsigned long long g_stream_prof[16];
-extern "C" int va_stream_prof_read(unsigned long long* host, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(host, g_stream_prof, sizeof(g_stream_prof));
-  if (e == cudaSuccess && reset) {
-    unsigned long long z[16] = {};
-    z[11] = ~0ull;
-    e = cudaMemcpyToSymbol(g_stream_prof, z, sizeof(z));
-  }
-  return e == cudaSuccess ? 0 : -1;
-}
-#define SPROF(stmt) stmt
-#else
-#define SPROF(stmt)
-#endif
-
 namespace {
 
 using namespace va;
@@ -257,7 +235,6 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
   // the merge pass may be made resident now; it waits for this grid to complete
   pdl_launch_dependents();
 
-  SPROF(unsigned long long pf[8] = {}; unsigned long long gt0; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt0)); const long long pc0 = clock64();)
   const int lane_id = blockIdx.x * Cfg::kWarps + wl;
   if (lane_id >= p.num_lanes) return;
   const int it_begin = p.lane_off[lane_id];
@@ -388,7 +365,6 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
     const int part = item[5];
     const int kvh = item[6];
     const int n_stages = (n_keys + kKeysPerStage - 1) / kKeysPerStage;
-    SPROF(long long pq0 = clock64(); pf[7] += 1;)
 
     // ---- stage the rotated queries of this kv head's GQA group: qs[8][D] (rows >= gqa are 0)
     stage_queries<D>(qs, p.q + static_cast<int64_t>(qrow) * p.q_row_stride +
@@ -405,7 +381,6 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
     }
     __syncwarp();  // qs may be overwritten by the next item's staging only after these reads
 
-    SPROF(pf[4] += clock64() - pq0;)
     float acc[KSTEPS][4];
 #pragma unroll
     for (int i = 0; i < KSTEPS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -414,7 +389,6 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
 
     for (int s = 0; s < n_stages; ++s, ++gs) {
       const int b = gs % NST;
-      SPROF(long long pw0 = clock64();)
       if (!mbar_wait_bounded(full_u32 + b * 8, (gs / NST) & 1u, kWaitPolls)) {
         // A bounded wait ran out.  Copies the producer issued may still land in this lane's ring:
         // give every barrier a bounded time, then stop working.
@@ -424,7 +398,6 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
         return;
       }
       __syncwarp();
-      SPROF(long long pc1 = clock64(); pf[1] += pc1 - pw0; pf[6] += 1;)
       const uint32_t sbase = ring_u32 + b * Sm::kStageBytes;
 
       // ---- S^T (16 keys x 8 heads) = K . Qrot^T, four accumulators to shorten the dependency chain
@@ -491,10 +464,8 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
         mma_bf16_16816(acc[mt], a, pb);
       }
       __syncwarp();  // every lane has read this stage
-      SPROF(pf[2] += clock64() - pc1;)
 
       if (s == n_stages - 1) {
-        SPROF(long long pp0 = clock64();)
         // ---- last stage: write the partial.  Reduce the sums over the 8 key groups, stage O^T as
         // [head][dim] in this stage's buffer (still owned by the consumer), copy it out.
 #pragma unroll
@@ -531,23 +502,10 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
         // the staging buffer was written through the generic proxy and is refilled by bulk copies
         fence_proxy_async();
         __syncwarp();
-        SPROF(pf[5] += clock64() - pp0;)
       }
       if (lane == 0) mbar_arrive(empty_u32 + b * 8);   // the producer may refill this stage
     }
   }
-#if VA_STREAM_PROF
-  if (lane == 0) {
-    pf[0] = clock64() - pc0;
-    unsigned long long gt1;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt1));
-    for (int i = 0; i < 8; ++i) atomicAdd(&g_stream_prof[i], pf[i]);
-    atomicMax(&g_stream_prof[8], gt1);
-    atomicAdd(&g_stream_prof[9], gt1 - gt0);
-    atomicAdd(&g_stream_prof[10], 1ull);
-    atomicMin(&g_stream_prof[11], gt0);
-  }
-#endif
 }
 
 // One warp per (query row, query head); the partials of (row, kv head) are contiguous:
@@ -724,10 +682,11 @@ extern "C" int va_decode_lanes(int32_t head_dim) {
   return VA_ERR_UNSUPPORTED;
 }
 
-extern "C" int va_view_decode(const VaPool* pool, const VaDecodePlan* plan, const void* q,
-                              int64_t q_row_stride, void* out, int64_t out_row_stride,
-                              float* partial_o, float* partial_ml, int32_t* status,
-                              va_stream_t stream) {
+namespace {
+// Argument checks of a decode step, shared by both entry points; nothing is launched on failure.
+int check_decode_args(const VaPool* pool, const VaDecodePlan* plan, const void* q, int64_t q_row_stride,
+                      const void* out, int64_t out_row_stride, const float* partial_o,
+                      const float* partial_ml) {
   int rc = va_host::check_pool(pool);
   if (rc != VA_OK) return rc;
   if (plan == nullptr || q == nullptr || out == nullptr) return VA_ERR_BAD_ARG;
@@ -745,11 +704,26 @@ extern "C" int va_view_decode(const VaPool* pool, const VaDecodePlan* plan, cons
         plan->num_lanes > va_decode_lanes(pool->head_dim))
       return VA_ERR_BAD_ARG;
   }
+  // the dense tiles of `groups` write into the same scratch: they may not name a slot beyond it
+  if (plan->groups != nullptr && plan->groups->num_tiles > 0 &&
+      plan->groups->num_partials > plan->num_partials)
+    return VA_ERR_CAPACITY;
   if ((reinterpret_cast<uintptr_t>(pool->k) | reinterpret_cast<uintptr_t>(pool->v) |
        reinterpret_cast<uintptr_t>(partial_o) | reinterpret_cast<uintptr_t>(q) |
        reinterpret_cast<uintptr_t>(out)) & 15)
     return VA_ERR_BAD_ARG;
   if ((q_row_stride & 7) || (out_row_stride & 1)) return VA_ERR_BAD_ARG;
+  return VA_OK;
+}
+}  // namespace
+
+extern "C" int va_view_decode(const VaPool* pool, const VaDecodePlan* plan, const void* q,
+                              int64_t q_row_stride, void* out, int64_t out_row_stride,
+                              float* partial_o, float* partial_ml, int32_t* status,
+                              va_stream_t stream) {
+  int rc = check_decode_args(pool, plan, q, q_row_stride, out, out_row_stride, partial_o, partial_ml);
+  if (rc != VA_OK) return rc;
+  if (plan->num_rows == 0) return VA_OK;
 
   DecodeParams p;
   p.k_pool = static_cast<const __nv_bfloat16*>(pool->k);
@@ -881,13 +855,24 @@ extern "C" int va_view_decode_static(const VaPool* pool, const VaDecodePlan* pla
   if (plan == nullptr) return VA_ERR_BAD_ARG;
   if (plan->num_partials < 0) return VA_ERR_BAD_ARG;
   const size_t gqa = static_cast<size_t>(pool->num_q_heads / pool->num_kv_heads);
-  const size_t need_heads = static_cast<size_t>(plan->num_partials) * gqa;
+  // the larger of the two partial counts the step names: the dense tiles bound their writes by their own
+  size_t partials = static_cast<size_t>(plan->num_partials);
+  if (plan->groups != nullptr && plan->groups->num_tiles > 0) {
+    if (plan->groups->num_partials < 0) return VA_ERR_BAD_ARG;
+    partials = partials > static_cast<size_t>(plan->groups->num_partials)
+                   ? partials : static_cast<size_t>(plan->groups->num_partials);
+  }
+  const size_t need_heads = partials * gqa;
   if (need_heads > kStaticMaxHeads || need_heads * static_cast<size_t>(pool->head_dim) > kStaticMaxFloats)
     return VA_ERR_CAPACITY;  // the plan does not fit the static scratch array
   float* partial_o = nullptr;
   float* partial_ml = nullptr;
   rc = static_scratch(&partial_o, &partial_ml);
   if (rc != VA_OK) return rc;
+  // every check of the regular entry point, before the dense tiles are launched
+  rc = check_decode_args(pool, plan, q, q_row_stride, out, out_row_stride, partial_o, partial_ml);
+  if (rc != VA_OK) return rc;
+  if (plan->num_rows == 0) return VA_OK;
   if (plan->groups != nullptr && plan->groups->num_tiles > 0 &&
       (plan->phase_mask & VA_PHASE_SKIP_GROUPS) == 0) {
     rc = va_view_dense(pool, plan->groups, q, q_row_stride, out, out_row_stride, partial_o, partial_ml,

@@ -40,21 +40,6 @@
 #ifndef VA_TC_WAIT_NS
 #define VA_TC_WAIT_NS 1000
 #endif
-#ifndef VA_TC_PROF
-#define VA_TC_PROF 0
-#endif
-#if VA_TC_PROF
-// profiling build only: cycles every role spent in each kind of wait
-__device__ unsigned long long g_tc_prof[3 * 16];
-extern "C" int va_tc_prof_read(unsigned long long* host, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(host, g_tc_prof, sizeof(g_tc_prof));
-  if (e == cudaSuccess && reset) {
-    unsigned long long z[3 * 16] = {};
-    e = cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z));
-  }
-  return e == cudaSuccess ? 0 : -1;
-}
-#endif
 
 namespace {
 
@@ -362,27 +347,16 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
   uint32_t ru[2] = {0u, 0u};
   bool dead = false;
   bool q_release_pending = false;  // MMA warp: the staged queries' QEmpty commit is still owed
-#if VA_TC_PROF
-  unsigned long long prof[16] = {};
-  const long long prof_t0 = clock64();
-  auto kind_of = [](int slot) { return slot < 2 ? slot : slot < 7 ? 2 : slot < 12 ? 4 : slot < 14 ? 5 : slot < 16 ? 7 : slot < 18 ? 8 : 6; };
-#endif
   // Bounded wait.  A role that gives up raises the CTA-wide abort flag, which every other wait
   // polls, so one expiry takes all roles out of their loops.
   auto wait = [&](int slot, uint32_t parity) -> bool {
     if (dead) return false;
     const uint32_t b = bar(slot);
-#if VA_TC_PROF
-    const long long w0 = clock64();
-#endif
     for (int i = 0; i < kTcPolls; ++i) {
 #if VA_TC_WAIT_NS > 0
       const bool done = mbar_try_wait_hint(b, parity & 1u, VA_TC_WAIT_NS);
 #else
       const bool done = mbar_try_wait(b, parity & 1u);
-#endif
-#if VA_TC_PROF
-      if (done) prof[kind_of(slot)] += static_cast<unsigned long long>(clock64() - w0);
 #endif
       if (done) return true;
       if ((i & 63) == 63 && *abort_flag != 0) break;
@@ -457,9 +431,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
         // ---- queries of this segment, rotated by rel + loc_base
         if (!reuse_q) {
         if (!wait(kBarQEmpty, (q_idx & 1u) ^ 1u)) break;
-#if VA_TC_PROF
-        const long long pq1 = clock64();
-#endif
         {
           const int loc_base = seg_field(s, 3);
           const int half = p.rotary_dim >> 1;
@@ -556,9 +527,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(kBarQFull));
           ++q_idx;
-#if VA_TC_PROF
-          prof[13] += static_cast<unsigned long long>(clock64() - pq1);
-#endif
         }
         }
         // ---- K and V tiles of this segment: this warp fills the ring units that map to its slot
@@ -593,9 +561,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
             }
             // the page-table reads above are in flight while the slot is still being consumed
             if (!wait(kBarEmpty + lw, ((u / NSLOT) & 1u) ^ 1u)) break;
-#if VA_TC_PROF
-            const long long pl1 = clock64();
-#endif
             // lanes run along a key's row (512 contiguous bytes per warp-wide copy: one row at
             // head_dim 256, two at 128)
             constexpr int kRowsPerCopy = 512 / (D * 2);
@@ -615,10 +580,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kBarFull + lw));
-#if VA_TC_PROF
-            prof[12] += static_cast<unsigned long long>(clock64() - pl1);
-            prof[14] += 1;
-#endif
           }
         }
       }
@@ -740,9 +701,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
     } else {
       // =========================================================== softmax (thread = query row)
       const int i_s = warp >> 2;                   // stream of this warp
-#if VA_TC_PROF
-      long long pe0 = 0;
-#endif
       if (i_s < n_streams) {
         const int row = i_s * kRows + (tid & 127);  // row of the CTA tile
         const int e = row / gqa;
@@ -769,9 +727,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
             const uint32_t s_addr = lane_addr + Cfg::kColS + r * BN;
             const int k0 = t * BN;
             const int vis = klim - k0;  // keys of this tile visible to the row: columns [0, vis)
-#if VA_TC_PROF
-            const long long pt1 = clock64();
-#endif
             // ---- maximum of the visible raw dot products, half a row at a time; the second
             // half stays in registers for the exponentials
             constexpr int NH = BN / 64;   // 32-column loads per half row
@@ -801,9 +756,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
               }
             }
             mx *= p.scale_log2;  // the scale is positive: max of scaled = scaled max
-#if VA_TC_PROF
-            prof[9] += static_cast<unsigned long long>(clock64() - pt1);
-#endif
             // ---- lazy rescale: move the offset only when the maximum grew a lot
             const bool grow = mx > m_used + kRescaleLog2 || (m_used == -INFINITY && mx > -INFINITY);
             float factor = 1.f;
@@ -811,10 +763,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
               factor = m_used == -INFINITY ? 0.f : fast_exp2(m_used - mx);
               m_used = mx;
             }
-#if VA_TC_PROF
-            const long long pt2 = clock64();
-            if (__any_sync(0xffffffffu, grow) && j > 0) prof[10] += 1;
-#endif
             if (__any_sync(0xffffffffu, grow) && j > 0) {
               // O may only be rescaled after the PV product of the previous key tile has finished
               // (products complete in issue order, so every earlier one has finished too)
@@ -871,16 +819,9 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kBarPFull + r));
-#if VA_TC_PROF
-            prof[11] += static_cast<unsigned long long>(clock64() - pt2);
-            prof[14] += 1;
-#endif
           }
         }
         // ---- epilogue: wait for the last PV product, then final rows or split-K partials
-#if VA_TC_PROF
-        pe0 = clock64();
-#endif
         if (!dead && total_kt > 0) {
           if (wait_warp(kBarPVDone + region_of(i_s, total_kt - 1), use_of(i_s, total_kt - 1) & 1u)) {
             tc_fence_after();
@@ -947,9 +888,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarOFree));
       }
-#if VA_TC_PROF
-      if (i_s < n_streams) prof[12] += static_cast<unsigned long long>(clock64() - pe0);
-#endif
     }
     // every role advances the shared counters the same way
     ku += 2u * static_cast<uint32_t>(total_kt);
@@ -981,13 +919,6 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
     }  // padding warps of the last warpgroup have no work
   }
 
-#if VA_TC_PROF
-  if (lane == 0) {
-    const int role = warp >= Cfg::kLoaderWarp0 ? 0 : warp == Cfg::kMmaWarp ? 1 : 2;
-    prof[15] = static_cast<unsigned long long>(clock64() - prof_t0);
-    for (int i = 0; i < 16; ++i) atomicAdd(&g_tc_prof[role * 16 + i], prof[i]);
-  }
-#endif
   tc_fence_before();
   __syncthreads();
   if (warp == Cfg::kMmaWarp) {

@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import ctypes as C
 import itertools
+import os
 from types import SimpleNamespace
 from dataclasses import dataclass, field
 from typing import Dict, List, Literal, Optional, Sequence
@@ -30,7 +31,7 @@ import torch
 
 from . import _lib
 from .attention_base import BaseAttnMetadata
-from .blocks import CacheBlock, WorkerGroup
+from .blocks import CacheBlock, WorkerGroup, block_page_numbers
 from .kvpool import pool_struct, store_rows
 
 DENSE_ENGINES = {"mma_sync": 0, "tcgen05": 1}
@@ -266,8 +267,12 @@ class SharedDecodeAttentionBuffers:
     """
 
     def __init__(self, attention: "SharedCacheAttention", workers: int, depth: int, max_pages: int,
-                 dense_fraction: float = 0.0):
+                 dummy_slots=None, *, dense_fraction: float = 0.0):
+        # positional arguments as the reference's class takes them (attention_graph.py:15; call site
+        # minisgl/shared_cache/graph.py:90-91).  `dummy_slots` (the reference's padding targets) is
+        # accepted and not needed: padding rows are empty ranges here and are never stored.
         a = self.attention = attention
+        self.dummy_slots = dummy_slots
         self.workers, self.depth, self.max_pages = workers, depth, max_pages
         H = a.num_kv_heads
         if a.device.type == "cuda":
@@ -431,6 +436,8 @@ class SharedCacheAttention:
         rotary_dim: Optional[int] = None,
         mrope_section: Optional[tuple] = None,
         rope_base: Optional[float] = None,
+        *,
+        dense_engine: Optional[str] = None,
     ) -> None:
         if mrope_section is not None and rope_base is None:
             raise ValueError("mrope_section needs rope_base (the rotation is defined by its frequencies)")
@@ -467,12 +474,11 @@ class SharedCacheAttention:
         elif cos_sin_cache is not None:
             self._cos_sin = cos_sin_cache.to(device=self.device, dtype=torch.float32).contiguous()
             assert self._cos_sin.shape[1] == self.rotary_dim, "cos_sin_cache must be [max_pos, rotary_dim]"
-        import os
-
-        # which tensor-core path runs dense tiles (prefill, shared-block decode)
-        self.dense_engine = os.environ.get("VIEWATTN_DENSE_ENGINE", "tcgen05")
+        # which tensor-core path runs dense tiles (prefill, shared-block decode): the keyword argument,
+        # else the VIEWATTN_DENSE_ENGINE environment variable, else tcgen05
+        self.dense_engine = dense_engine or os.environ.get("VIEWATTN_DENSE_ENGINE", "tcgen05")
         if self.dense_engine not in DENSE_ENGINES:
-            raise ValueError(f"VIEWATTN_DENSE_ENGINE must be one of {sorted(DENSE_ENGINES)}")
+            raise ValueError(f"dense_engine must be one of {sorted(DENSE_ENGINES)}")
         self._lanes: Optional[int] = None
         self._sm_count: Optional[int] = None
         self._topology: Optional[_ViewTopology] = None   # flattened views of the last planned group
@@ -518,17 +524,27 @@ class SharedCacheAttention:
             raise RuntimeError(f"view attention kernel reported {_lib.DEVICE_CODES.get(code, code)}")
 
     def prepare_workspace(self, profiles) -> None:
-        """Reserve scratch for the largest profile before graph capture (no-op if none)."""
+        """Reserve the split-K scratch of the largest profile before graph capture (no-op if none).
+
+        A profile is a fixed-capacity buffer object (``SharedDecodeAttentionBuffers`` /
+        ``SharedPrefillAttentionBuffers``), as in the reference
+        (minisgl/shared_cache/attention.py:212-239): it must belong to this instance, and the call
+        must come before capture."""
         profiles = tuple(profiles)
-        for p in profiles:
-            need = getattr(p, "max_items", None)
-            if need:
-                self._reserve_partials(int(need))
+        if not profiles:
+            return
+        if self.device.type == "cuda" and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("Attention workspace must be prepared once before capture")
+        if any(getattr(p, "attention", self) is not self for p in profiles):
+            raise ValueError("Attention workspace profiles must belong to this instance")
+        need = max(int(getattr(p, "cap_partials", 0) or getattr(p, "max_items", 0) or 0) for p in profiles)
+        if need:
+            self._reserve_partials(need)
 
     def _reserve_partials(self, n_items: int) -> None:
         cap = 0 if self._partial_o is None else self._partial_o.shape[0]
         if n_items > cap:
-            if torch.cuda.is_current_stream_capturing():
+            if self.device.type == "cuda" and torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("Attention workspace must be prepared once before capture")
             new_cap = max(n_items, int(cap * 1.5), 1024)
             self._partial_o = torch.empty(new_cap, self.gqa, self.head_dim, dtype=torch.float32, device=self.device)
@@ -625,7 +641,7 @@ class SharedCacheAttention:
         # block keeps its page numbers as an array until its page list changes); a page allocated
         # for this step's token is the last page of its block's run
         lens = blk_len.tolist()
-        runs = [b.page_numbers() if n else _NO_PAGES for b, n in zip(blocks, lens)]
+        runs = [block_page_numbers(b) if n else _NO_PAGES for b, n in zip(blocks, lens)]
         run_len = np.fromiter([r.size for r in runs], np.int32, nb)
         index = topo.index
         pending_page = None
@@ -871,8 +887,7 @@ class SharedCacheAttention:
                 run = block_run.get(key)
                 if run is None:
                     run = block_run[key] = n_pages
-                    pages = block.page_numbers() if block.page_size == P else (
-                        np.asarray(block.page_starts, np.int64) // block.page_size)
+                    pages = block_page_numbers(block)
                     page_parts.append(pages)
                     n_pages += pages.size
                 ctx_snap.append((run, block.num_pages, block.num_tokens, block.last_page_len, span))

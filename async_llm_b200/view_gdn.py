@@ -111,21 +111,25 @@ class SharedCacheGDN:
         """Device addresses ``[layers, 2]`` of a block's (A_hat, B_hat) per layer, 0 where it has
         none.  Kept on the block until one of its state dictionaries changes (the reference caches
         the same addresses behind its StateDict, minisgl/shared_cache/gdn_state.py:15-58)."""
-        c = block._gdn_ptr_cache
-        if c is None or c[0] != block._gdn_revision or c[1] != self.device or c[2].shape[0] < layers:
+        rev = getattr(block, "_gdn_revision", None)
+        c = getattr(block, "_gdn_ptr_cache", None) if rev is not None else None
+        if c is None or c[0] != rev or c[1] != self.device or c[2].shape[0] < layers:
             held: list = []
             ptrs = np.zeros((layers, 2), np.int64)
             for layer in range(layers):
                 ptrs[layer] = self._pair_ptrs(block, layer, held)
-            c = block._gdn_ptr_cache = (block._gdn_revision, self.device, ptrs, held)
+            c = (rev, self.device, ptrs, held)
+            if rev is not None:   # a block without a revision counter (the reference's own class) is re-read
+                block._gdn_ptr_cache = c
         keep.append(c[3])
         return c[2][:layers]
 
     def _block_conv_ptrs(self, block: CacheBlock, layers: int, keep: list) -> np.ndarray:
         """Device addresses ``[layers]`` of a block's conv windows (bf16 ``[conv_dim, k]``), 0 where
         it has none; kept on the block like the summary addresses."""
-        c = block._gdn_conv_cache
-        if c is None or c[0] != block._gdn_revision or c[1] != self.device or c[2].shape[0] < layers:
+        rev = getattr(block, "_gdn_revision", None)
+        c = getattr(block, "_gdn_conv_cache", None) if rev is not None else None
+        if c is None or c[0] != rev or c[1] != self.device or c[2].shape[0] < layers:
             held: list = []
             ptrs = np.zeros(layers, np.int64)
             for layer, state in block.linear_conv_state.items():
@@ -135,7 +139,9 @@ class SharedCacheGDN:
                     t = state.to(device=self.device, dtype=torch.bfloat16).contiguous()
                     held.append(t)
                     ptrs[layer] = t.data_ptr()
-            c = block._gdn_conv_cache = (block._gdn_revision, self.device, ptrs, held)
+            c = (rev, self.device, ptrs, held)
+            if rev is not None:
+                block._gdn_conv_cache = c
         keep.append(c[3])
         return c[2][:layers]
 
@@ -253,6 +259,8 @@ class SharedCacheGDN:
                 if st["conv_layers"]:
                     conv_rows = st["conv_out"][w].unbind(0)
                     target.linear_conv_state.update({layer: conv_rows[layer] for layer in st["conv_layers"]})
+                if not hasattr(target, "_gdn_revision"):
+                    continue
                 if len(target.linear_affine) == layers:
                     target._gdn_ptr_cache = (target._gdn_revision, self.device, new_ptrs[w], [slab_a, slab_b])
                 if len(st["conv_layers"]) == layers and len(target.linear_conv_state) == layers:

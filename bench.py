@@ -145,7 +145,7 @@ def cpu_step_seconds(case, repeats: int):
 def run_reference(args, rank: int) -> None:
     if rank != 0:
         return
-    from async_llm_b200 import workloads as wl
+    import benchcases as wl
 
     torch.set_num_threads(os.cpu_count() or 1)
     case = wl.config2_decode(page_size=PAGE_SIZE, requests=REQUESTS, shared_len=SHARED_LEN,
@@ -206,7 +206,7 @@ def time_plain(fn, iters: int) -> float:
 def run_side_workload(args, device) -> None:
     """Other rows of the scope table, one JSON line each (not the headline metric):
     view prefill (config 3), GDN decode step (config 4b), GDN prefill scan (config 4a)."""
-    from async_llm_b200 import workloads as wl
+    import benchcases as wl
 
     peaks = {}
     try:
@@ -374,7 +374,8 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device: the cache-view path has no CPU fallback")
     import torch.distributed as dist
 
-    from async_llm_b200 import _lib, workloads as wl
+    from async_llm_b200 import _lib
+    import benchcases as wl
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)

@@ -12,7 +12,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from .blocks import CacheBlock, WorkerGroup
+from async_llm_b200.blocks import CacheBlock, WorkerGroup
 
 
 def cos_sin_table(rotary_dim: int, max_pos: int, base: float) -> torch.Tensor:
@@ -183,11 +183,11 @@ def config2_decode(page_size: int = 16, seed: int = 2000, requests: int = 64,
 class DeviceView:
     """A ``ViewCase`` resident on one GPU behind the public pool / attention classes."""
 
-    def __init__(self, case: ViewCase, device: torch.device, num_layers: int = 1):
+    def __init__(self, case: ViewCase, device: torch.device, num_layers: int = 1, dense_engine=None):
         from types import SimpleNamespace
 
-        from .kvpool import MHAKVCache
-        from .view_attention import SharedCacheAttention
+        from async_llm_b200.kvpool import MHAKVCache
+        from async_llm_b200.view_attention import SharedCacheAttention
 
         self.case = case
         self.device = torch.device(device)
@@ -198,7 +198,7 @@ class DeviceView:
             self.pool.v_cache(layer).copy_(case.v_pool)
         self.attn = SharedCacheAttention(
             self.pool, case.cos_sin.to(self.device), case.num_q_heads, case.num_kv_heads,
-            case.head_dim, case.page_size, torch.bfloat16, self.device,
+            case.head_dim, case.page_size, torch.bfloat16, self.device, dense_engine=dense_engine,
         )
         self.q = case.q.to(self.device)
         self.k_new = case.k_new.to(self.device)
@@ -240,7 +240,7 @@ class PrefillCase:
     self_pages: List[torch.Tensor]  # per request: complete post-write page-start list of its block
 
     def specs(self):
-        from .view_attention import PrefillSpec
+        from async_llm_b200.view_attention import PrefillSpec
 
         out = []
         for req, pages in zip(self.requests, self.self_pages):
@@ -338,11 +338,11 @@ def config3_prefill(page_size: int = 16, seed: int = 3000, requests: int = 16, c
 class DevicePrefill:
     """A ``PrefillCase`` resident on one GPU behind the public pool / attention classes."""
 
-    def __init__(self, case: PrefillCase, device: torch.device):
+    def __init__(self, case: PrefillCase, device: torch.device, dense_engine=None):
         from types import SimpleNamespace
 
-        from .kvpool import MHAKVCache
-        from .view_attention import SharedCacheAttention
+        from async_llm_b200.kvpool import MHAKVCache
+        from async_llm_b200.view_attention import SharedCacheAttention
 
         self.case = case
         self.device = torch.device(device)
@@ -352,7 +352,7 @@ class DevicePrefill:
         self.pool.v_cache(0).copy_(case.v_pool)
         self.attn = SharedCacheAttention(self.pool, case.cos_sin.to(self.device), case.num_q_heads,
                                          case.num_kv_heads, case.head_dim, case.page_size,
-                                         torch.bfloat16, self.device)
+                                         torch.bfloat16, self.device, dense_engine=dense_engine)
         self.q, self.k_new, self.v_new = (t.to(self.device) for t in (case.q, case.k_new, case.v_new))
         self._ns = SimpleNamespace
 

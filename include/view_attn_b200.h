@@ -2,8 +2,12 @@
  * view_attn_b200.h -- C ABI of the B200 (sm_100a) cache-view attention / Gated DeltaNet kernels.
  *
  * Every entry point takes plain device pointers and sizes, launches on the given CUDA stream,
- * allocates nothing, keeps no reference to caller memory and never throws: it returns 0 or a
- * negative VA_ERR_* code.  The caller (PyTorch host code, or any other runtime) owns all memory.
+ * allocates no device memory, keeps no reference to caller memory and never throws: it returns 0
+ * or a negative VA_ERR_* code.  The caller (PyTorch host code, or any other runtime) owns all
+ * memory.  The only driver objects the library creates are one non-blocking side stream and two
+ * events per device, on the first va_view_decode call whose plan carries shared-block tiles
+ * (`groups`); va_view_decode_static creates none.  Kernels that need more than 48 KB of shared
+ * memory opt in with cudaFuncSetAttribute on the launching call.
  * Device-side faults (a page index outside the pool, a bounded wait that ran out) are reported
  * through the caller-supplied `status` word: 0 = clean, otherwise the first VA_DEV_* code seen.
  *
@@ -291,7 +295,9 @@ int va_gdn_prefill(const VaGdnPrefill* args, va_stream_t stream);
  * device memory (a process that gave all free HBM to its KV pool at start-up; a host without a
  * device allocator): the split-K scratch is a fixed array inside the library, present on every GPU
  * that loads it.  Limits: num_partials * G * head_dim <= 2048*8*256 floats and num_partials * G <=
- * 2048*8 (G = num_q_heads/num_kv_heads), else VA_ERR_CAPACITY and nothing is launched.  The first
+ * 2048*8 (G = num_q_heads/num_kv_heads; num_partials = the larger of the plan's and its `groups`'),
+ * else VA_ERR_CAPACITY; every argument check of va_view_decode runs before the first launch, so a
+ * refused call launches nothing.  The first
  * call on a device looks up the array's device address and should be made outside stream capture.
  * All calls on one GPU share the array: calls that may overlap on the GPU race; calls queued on one
  * stream do not.  The array keeps the previous call's contents and needs no clearing (every slot a

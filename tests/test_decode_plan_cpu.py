@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from async_llm_b200 import workloads as wl
+import benchcases as wl
 from async_llm_b200.view_attention import SharedCacheAttention
 from helpers import oracle_decode
 from oracle import view_oracle as vo

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from async_llm_b200 import MHAKVCache, SharedCacheAttention
-from async_llm_b200 import workloads as wl
+import benchcases as wl
 from helpers import assert_close_bf16
 from oracle import view_oracle as vo
 
@@ -75,7 +75,7 @@ def test_prefill_with_three_axis_query_positions(cuda_device):
     # two requests; the first one's new tokens are an image patch grid (per-axis positions), the
     # second one's are text.  Keys enter the pool rotated per axis, queries are rotated per axis
     # inside the dense-tile kernel; the causal mask stays on token indices.
-    from async_llm_b200.workloads import make_prefill_case
+    from benchcases import make_prefill_case
     rd, section, base = 64, (11, 11, 10), 1e6
     case = make_prefill_case(lengths={"sys": 200, "doc": 333, "a": 5, "b": 0},
                              requests=[{"context": ["sys", "doc"], "write": "a", "num_new": 70},

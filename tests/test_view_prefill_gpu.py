@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from async_llm_b200 import workloads as wl
+import benchcases as wl
 from helpers import assert_close_bf16, oracle_prefill
 
 pytestmark = pytest.mark.gpu

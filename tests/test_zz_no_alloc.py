@@ -12,7 +12,8 @@ import ctypes as C
 import pytest
 import torch
 
-from async_llm_b200 import _lib, workloads as wl
+from async_llm_b200 import _lib
+import benchcases as wl
 from async_llm_b200.kvpool import pool_struct
 from helpers import assert_close_bf16
 
