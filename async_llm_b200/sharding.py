@@ -141,17 +141,25 @@ class BlockReplicator:
         meta = [None]
         if self.rank == src:
             total = block.num_tokens if total_tokens is None else total_tokens
+            gdn = []
+            for layer in gdn_layers:
+                pair = block.linear_affine.get(layer)
+                conv = block.linear_conv_state.get(layer)
+                if pair is None and conv is None:
+                    continue
+                gdn.append((layer,
+                            None if pair is None else (tuple(pair[0].shape), tuple(pair[1].shape), str(pair[0].dtype)),
+                            None if conv is None else (tuple(conv.shape), str(conv.dtype))))
             meta = [{"total": total, "span": block.mrope_span_override,
-                     "token_ids": list(block.token_ids[first_token:total]),
-                     "gdn": [layer for layer in gdn_layers if layer in block.linear_affine]}]
+                     "token_ids": list(block.token_ids[first_token:total]), "gdn": gdn}]
         dist.broadcast_object_list(meta, src=src, group=self.group)
         info = meta[0]
         total = info["total"]
         n_new = total - first_token
         layers = self.kv_cache.num_layers
         k0, _ = self._flat(0)
-        stage = torch.empty(layers, 2, max(n_new, 0), k0.shape[1], k0.shape[2], dtype=k0.dtype, device=device)
         if n_new > 0:
+            stage = torch.empty(layers, 2, n_new, k0.shape[1], k0.shape[2], dtype=k0.dtype, device=device)
             if self.rank == src:
                 slots = block.token_slots_tensor().to(device).long()[first_token:total]
                 for layer in range(layers):
@@ -164,32 +172,47 @@ class BlockReplicator:
                 assert block.num_tokens == first_token, "replica is missing earlier tokens of the block"
                 fresh = self.page_allocator.alloc_pages(block.pages_needed(n_new))
                 block.grow_pages(fresh, n_new)
-                block.token_ids.extend(info["token_ids"])
-                block.mrope_span_override = info["span"]
                 slots = block.token_slots_tensor().to(device).long()[first_token:total]
                 for layer in range(layers):
                     kf, vf = self._flat(layer)
                     kf[slots] = stage[layer, 0]
                     vf[slots] = stage[layer, 1]
-        for layer in info["gdn"]:
-            if self.rank == src:
-                a, b = (t.to(device).contiguous() for t in block.linear_affine[layer])
-            else:
-                ref_a = ref_b = None
-                a = b = None
-            shapes = [None]
-            if self.rank == src:
-                shapes = [(tuple(a.shape), tuple(b.shape), str(a.dtype))]
-            dist.broadcast_object_list(shapes, src=src, group=self.group)
-            sa, sb, dt = shapes[0]
-            dtype = getattr(torch, dt.split(".")[-1])
-            if self.rank != src:
-                a = torch.empty(sa, dtype=dtype, device=device)
-                b = torch.empty(sb, dtype=dtype, device=device)
-            dist.broadcast(a, src=src, group=self.group)
-            dist.broadcast(b, src=src, group=self.group)
-            if self.rank != src:
-                block.linear_affine[layer] = (a, b)
+        if self.rank != src:
+            # bookkeeping that does not depend on new rows having been sent (a publish may only
+            # refresh the span or the recurrent state of a block whose tokens are already here)
+            block.token_ids.extend(info["token_ids"])
+            block.mrope_span_override = info["span"]
+
+        def as_dtype(name: str) -> torch.dtype:
+            return getattr(torch, name.split(".")[-1])
+
+        # GDN state of the published layers: the affine pair and the conv window a reader of the
+        # replica needs to continue the block (minisgl/shared_cache/gdn.py:127-207)
+        for layer, pair_info, conv_info in info["gdn"]:
+            if pair_info is not None:
+                sa, sb, dt = pair_info
+                if self.rank == src:
+                    a, b = (t.to(device).contiguous() for t in block.linear_affine[layer])
+                else:
+                    a = torch.empty(sa, dtype=as_dtype(dt), device=device)
+                    b = torch.empty(sb, dtype=as_dtype(dt), device=device)
+                dist.broadcast(a, src=src, group=self.group)
+                dist.broadcast(b, src=src, group=self.group)
+                if self.rank == src:
+                    self.bytes_sent += (a.numel() + b.numel()) * a.element_size()
+                else:
+                    block.linear_affine[layer] = (a, b)
+            if conv_info is not None:
+                sc, dt = conv_info
+                if self.rank == src:
+                    c = block.linear_conv_state[layer].to(device).contiguous()
+                else:
+                    c = torch.empty(sc, dtype=as_dtype(dt), device=device)
+                dist.broadcast(c, src=src, group=self.group)
+                if self.rank == src:
+                    self.bytes_sent += c.numel() * c.element_size()
+                else:
+                    block.linear_conv_state[layer] = c
 
 
 __all__ = ["Partition", "partition_contexts", "BlockReplicator"]

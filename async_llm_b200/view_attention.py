@@ -673,6 +673,7 @@ class SharedCacheAttention:
         n_main, widest = info.num_main, info.max_segments
         n_sub = n_main + n_aux
         sub_out = subs[:, :n_sub].astype(np.int64)       # a copy: the next step reuses the buffer
+        self._check_positions(int(sub_out[1].max()) if n_sub else 0, "a query's distance to a view block")
         meta = SharedCacheAttnMetadata(
             shared_cache_op=self,
             sub_worker_list=sub_out[0],
@@ -692,6 +693,13 @@ class SharedCacheAttention:
         if graph_buffers is not None:
             meta.num_workers = graph_buffers.workers
         return meta
+
+    def _check_positions(self, largest: int, what: str) -> None:
+        """The kernels clamp a rotation distance to the last row of the cos/sin table, as
+        ``apply_rope_correction`` does (minisgl/shared_cache/rope_correction.py:36); a view longer
+        than the table would be rotated wrongly without any signal, so the planners refuse it."""
+        if self._cos_sin is not None and largest >= self._cos_sin.shape[0]:
+            raise ValueError(f"{what} ({largest}) reaches beyond the RoPE table ({self._cos_sin.shape[0]} positions)")
 
     # Planner constants of the streaming / dense-tile split (per-SM key rates, keys per microsecond
     # for one (reader, kv head) unit resp. one (reader group, kv head) tile row), by head_dim.
@@ -805,7 +813,6 @@ class SharedCacheAttention:
         mrope_positions = getattr(batch, "mrope_positions", None)
         if mrope_positions is not None and self.mrope_section is None:
             raise ValueError("batch.mrope_positions needs an attention op built with mrope_section")
-        rows = meta.num_workers
         if meta._pos32 is None:
             # [rows], or [3, rows] when the write does not sit at one position on all three axes
             pos = batch.positions if mrope_positions is None else mrope_positions
@@ -814,9 +821,15 @@ class SharedCacheAttention:
         store_rows(self.kv_cache, k, v, batch.out_loc, layer_id, meta._pos32, self._cos_sin,
                    self.rotary_dim, status=status,
                    mrope_lims=self._mrope_lims if self.mrope_section is not None else None)
+        return self._attend(q, meta, layer_id)
+
+    def _attend(self, q: torch.Tensor, meta: SharedCacheAttnMetadata, layer_id: int) -> torch.Tensor:
+        """The attention of a planned step over keys that are already in the pool."""
         if meta.phase == "prefill_batch":
             return self._forward_prefill_batch(q, meta, layer_id)
 
+        rows = meta.num_workers
+        status = self.status()
         plan: DecodePlan = meta.plan
         self._reserve_partials(plan.num_partials)
         q2 = q.reshape(rows, -1)
@@ -871,6 +884,7 @@ class SharedCacheAttention:
             T_span = T if spec.self_prefix_span is None else int(spec.self_prefix_span)
             spans = [b.mrope_span for b in spec.context]
             start = sum(spans) + T_span          # running position of the first new token
+            self._check_positions(start + S - 1, "a new token's position in its view")
             seg_begin = len(segments)
             before = 0
             if use_3d:

@@ -12,12 +12,17 @@ Pinning status
                          vectors ``tests/golden/rope_*.npz`` (generated from the reference).
 * ``plan_decode`` / ``plan_prefill`` -- PINNED: equal to the tables the reference planners emit
                          (minisgl/shared_cache/attention.py:282-622), golden ``tests/golden/plan_*.json``.
-* ``view_decode`` / ``view_prefill`` -- PARITY UNPINNED: the reference has no CPU-runnable
-  attention core (it calls the third-party ``flashinfer-python==0.6.17`` paged decode/prefill
-  kernels and ``merge_states``), and ships no golden outputs for it.  This restates the published
-  semantics of those calls -- softmax(q.k^T / sqrt(D)) in fp32 over each paged segment, outputs
-  combined by log-sum-exp weights, which equals one softmax over the concatenated view -- at the
-  reference's own call sites (attention.py:4-41 module docstring, :624-752).
+* ``view_decode`` / ``view_prefill`` -- PINNED on ``tests/golden/attention_golden.npz``: output rows
+  of the unmodified reference ``SharedCacheAttention.prepare`` / ``prepare_prefill_batch`` +
+  ``forward`` (minisgl/shared_cache/attention.py:282-752; its attention core is the third-party
+  ``flashinfer`` paged decode / prefill kernels with backend "fa2" and ``merge_states``) run on a
+  B200 on the seeded cases of ``tests/attention_cases.py`` by ``tests/golden/make_attention_golden.py``
+  (FlashInfer 0.6.11.post2 -- the reference pins 0.6.17 -- and the reference's own ``MHAKVCache``
+  store kernel).  ``tests/test_attention_golden_cpu.py`` compares this restatement with those rows
+  (max-abs 1e-4 .. 4e-3, i.e. one bf16 step of the output magnitude; the keys it stores are equal bit
+  for bit).  The restatement: softmax(q.k^T / sqrt(D)) in fp32 over each paged segment, outputs
+  combined by log-sum-exp weights, which equals one softmax over the concatenated view
+  (attention.py:4-41 module docstring, :624-752).
 """
 
 from __future__ import annotations

@@ -204,3 +204,20 @@ def test_replanning_consecutive_steps_reuses_the_view_structure():
     got = replay(case, a.prepare(group, pending, slots).plan, k_pool, v_pool)
     torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-4)
     assert len(a._topology.view_blk) == 8
+
+
+def test_planners_refuse_views_longer_than_the_rope_table():
+    # a rotation distance beyond the cos/sin table would be clamped silently by the kernels (and by
+    # the reference's apply_rope_correction): both planners raise instead
+    case = wl.config2_decode(page_size=16, requests=3, shared_len=300, private_len=70,
+                             num_q_heads=8, num_kv_heads=2, head_dim=128)
+    short = case.cos_sin[:200]
+    a = SharedCacheAttention(None, short, 8, 2, 128, 16, torch.bfloat16, torch.device("cpu"))
+    a._lanes, a._lane_width = 64, 4
+    pending, slots, _ = case.plan_writes()
+    with pytest.raises(ValueError, match="RoPE table"):
+        a.prepare(case.group, pending, slots)
+    from async_llm_b200 import PrefillSpec
+    spec = PrefillSpec([case.blocks["shared"]], torch.tensor([0, 16], dtype=torch.int32), 20, 0, None)
+    with pytest.raises(ValueError, match="RoPE table"):
+        a.prepare_prefill_batch([spec])

@@ -82,7 +82,7 @@ def build(topo, P):
 
 
 def cpu_attention(P):
-    a = SharedCacheAttention(None, vo.make_cos_sin_cache(64, 64, 1e4), 8, 2, 64, P, torch.bfloat16,
+    a = SharedCacheAttention(None, vo.make_cos_sin_cache(64, 4096, 1e4), 8, 2, 64, P, torch.bfloat16,
                              torch.device("cpu"))
     a._lanes = 16
     return a

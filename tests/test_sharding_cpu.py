@@ -75,12 +75,24 @@ def _replicate_worker(rank, world, port, out):
         if rank == 0:
             write(0, 37)
             block.linear_affine[1] = (torch.full((1, 2, 4, 4), 3.0), torch.full((1, 2, 4, 4), 5.0))
+            block.linear_conv_state[1] = torch.full((6, 4), 7.0, dtype=torch.bfloat16)
+            block.mrope_span_override = 30
         rep.publish(block, src=0, gdn_layers=(0, 1))
+        ok0 = block.mrope_span == 30
         if rank == 0:
             write(37, 42)
+            block.mrope_span_override = 33
         rep.publish(block, src=0, first_token=37)
+        ok0 &= block.mrope_span == 33
+        if rank == 0:
+            # a publish without new rows still refreshes the span and the recurrent state
+            block.mrope_span_override = 34
+            block.linear_conv_state[1] = torch.full((6, 4), 9.0, dtype=torch.bfloat16)
+        rep.publish(block, src=0, first_token=42, gdn_layers=(1,))
+        ok0 &= block.mrope_span == 34 and float(block.linear_conv_state[1].float().mean()) == 9.0
         slots = block.token_slots_tensor().long()
-        ok = block.num_tokens == 42 and block.token_ids == list(range(42))
+        ok = ok0 and block.num_tokens == 42 and block.token_ids == list(range(42))
+        ok &= 1 in block.linear_conv_state and 0 not in block.linear_conv_state
         for layer in range(layers):
             ok &= torch.equal(pool.k_cache(layer).view(-1, hkv, d)[slots], rows[layer, 0])
             ok &= torch.equal(pool.v_cache(layer).view(-1, hkv, d)[slots], rows[layer, 1])

@@ -8,8 +8,11 @@ from helpers import assert_close_bf16, oracle_decode
 pytestmark = pytest.mark.gpu
 
 
-def run_case(case, device):
-    dv = wl.DeviceView(case, device)
+ENGINES = ["tcgen05", "mma_sync"]   # the two tensor-core paths behind the shared-block tiles
+
+
+def run_case(case, device, dense_engine=None):
+    dv = wl.DeviceView(case, device, dense_engine=dense_engine)
     out = dv.decode()
     torch.cuda.synchronize()
     dv.attn.check_status()
@@ -26,11 +29,22 @@ def test_config1_three_block_views(cuda_device, page_size):
     run_case(wl.config1_decode(page_size=page_size), cuda_device)
 
 
+@pytest.mark.parametrize("engine", ENGINES)
 @pytest.mark.parametrize("page_size", [1, 16])
-def test_shared_prefix_small(cuda_device, page_size):
+def test_shared_prefix_small(cuda_device, page_size, engine):
     # the shared-prefix topology of the roofline configuration at a size the oracle finishes fast
     case = wl.config2_decode(page_size=page_size, requests=6, shared_len=700, private_len=333)
-    run_case(case, cuda_device)
+    dv, _ = run_case(case, cuda_device, engine)
+    assert dv.attn.dense_engine == engine
+
+
+@pytest.mark.parametrize("engine", ENGINES)
+def test_config2_full_size(cuda_device, engine):
+    # the benchmark configuration itself: 64 requests x [shared 8192 | private 2048], Hq16/Hkv2/D256,
+    # streaming lanes for the private blocks, dense tiles for the shared block, one merge
+    case = wl.config2_decode(page_size=16)
+    dv, out = run_case(case, cuda_device, engine)
+    assert out.shape == (64, 16 * 256)
 
 
 def test_edge_topologies(cuda_device):
@@ -56,13 +70,14 @@ def test_repeated_forward_is_deterministic(cuda_device):
     assert torch.equal(a, b)
 
 
-def test_scratch_left_poisoned_does_not_reach_the_output(cuda_device):
+@pytest.mark.parametrize("engine", ENGINES)
+def test_scratch_left_poisoned_does_not_reach_the_output(cuda_device, engine):
     # the split-K scratch keeps whatever an earlier step left in it: every slot the merge pass reads
     # must have been written by this step's items / tiles.  Poison it with NaN and decode a step that
     # uses both the streaming lanes and the dense tiles of a shared block.
     case = wl.config2_decode(page_size=16, requests=12, shared_len=700, private_len=90,
                              num_q_heads=8, num_kv_heads=2, head_dim=128)
-    dv = wl.DeviceView(case, cuda_device)
+    dv = wl.DeviceView(case, cuda_device, dense_engine=engine)
     batch = dv.plan()
     assert batch.attn_metadata.plan.groups is not None
     clean = dv.decode(batch).clone()

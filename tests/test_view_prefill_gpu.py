@@ -8,8 +8,12 @@ from helpers import assert_close_bf16, oracle_prefill
 pytestmark = pytest.mark.gpu
 
 
-def run_case(case, device):
-    dp = wl.DevicePrefill(case, device)
+ENGINES = ["tcgen05", "mma_sync"]   # the two tensor-core paths of the dense tiles
+
+
+def run_case(case, device, dense_engine=None):
+    dp = wl.DevicePrefill(case, device, dense_engine=dense_engine)
+    assert dense_engine is None or dp.attn.dense_engine == dense_engine
     out = dp.forward()
     torch.cuda.synchronize()
     dp.attn.check_status()
@@ -19,8 +23,9 @@ def run_case(case, device):
     assert_close_bf16(out, want, "view prefill")
 
 
+@pytest.mark.parametrize("engine", ENGINES)
 @pytest.mark.parametrize("page_size", [1, 16, 64])
-def test_small_view_prefill(cuda_device, page_size):
+def test_small_view_prefill(cuda_device, page_size, engine):
     # ragged chunk sizes, a request without context, a write block that already holds a prefix
     lengths = {"a": 70, "b": 129, "c": 5, "w0": 0, "w1": 37, "w2": 0}
     reqs = [{"context": ["a", "b"], "write": "w0", "num_new": 45},
@@ -29,14 +34,23 @@ def test_small_view_prefill(cuda_device, page_size):
     for D, hq, hkv in ((128, 8, 2), (256, 8, 1)):
         case = wl.make_prefill_case(lengths=lengths, requests=reqs, num_q_heads=hq, num_kv_heads=hkv,
                                     head_dim=D, page_size=page_size, rope_base=1e6, seed=5)
-        run_case(case, cuda_device)
+        run_case(case, cuda_device, engine)
 
 
-def test_config3_reduced(cuda_device):
+@pytest.mark.parametrize("engine", ENGINES)
+def test_config3_reduced(cuda_device, engine):
     # the benchmark topology (shared pool of context blocks, 2-6 blocks per request) at a size the
     # CPU oracle finishes in seconds
     case = wl.config3_prefill(requests=4, chunk=96, pool_blocks=6, min_len=100, max_len=400,
                               max_context=1400)
+    run_case(case, cuda_device, engine)
+
+
+def test_config3_four_requests_at_full_chunk_size(cuda_device):
+    # the benchmark's own request shape -- 512 new tokens against 2-6 context blocks of 1K-8K tokens,
+    # Hq32/Hkv8/D128 -- for the first 4 of its 16 requests (the CPU oracle needs seconds per request)
+    case = wl.config3_prefill(requests=4)
+    assert all(r["num_new"] == 512 for r in case.requests)
     run_case(case, cuda_device)
 
 
