@@ -181,11 +181,14 @@ def register(name: str = "b200") -> bool:
     except Exception:   # noqa: BLE001 -- the host framework is optional
         return False
 
-    @SUPPORTED_ATTENTION_BACKENDS.register(name)
+    if name in SUPPORTED_ATTENTION_BACKENDS.supported_names():
+        return True
+
     def create_b200_backend(config):
         ctx = get_global_ctx()
         return B200AttnBackend(config, ctx.kv_cache, lambda: get_global_ctx().page_table)
 
+    SUPPORTED_ATTENTION_BACKENDS.register(name)(create_b200_backend)
     return True
 
 

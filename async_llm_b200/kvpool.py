@@ -124,7 +124,7 @@ def _describe_pool(kv_cache, layer_id, num_q_heads, cos_sin, rotary_dim, sm_scal
     assert kc.is_contiguous() and vc.is_contiguous(), "per-layer pool views must be contiguous"
     pages, page_size, hkv, d = kc.shape
     if cos_sin is None:
-        key = kc.device
+        key = (kc.device, d)
         if key not in _DUMMY_COS_SIN:
             row = torch.zeros(1, d, dtype=torch.float32, device=kc.device)
             row[:, : d // 2] = 1.0

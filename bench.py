@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the cache-view decode hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
 
 A step is one pass of the view-decode path of one attention layer over one batch of requests:
 rotate-and-store of the new keys/values, the split-K walk over every request's view, the merge.
@@ -10,14 +10,20 @@ shared 8192-token block plus a private 2048-token block each (Hq16 / Hkv2 / head
 page size 16, page tables drawn from a random permutation of pool pages).
 
 One JSON line is printed by rank 0:
-  value      tokens/s with inputs and plan tables resident in HBM (CUDA events, max over ranks)
+  value      tokens/s with inputs and plan tables resident in HBM: the step is replayed from a CUDA
+             graph in rounds of exactly ``--steps`` replays between two CUDA events; ms_per_step is the
+             median round (max over ranks), enough rounds are timed to cover at least 100 ms
   e2e        tokens/s through the public API with HOST buffers: per step the pinned q/k/v rows go
-             host->device, the step is planned (SharedCacheAttention.prepare), run, and the output
-             rows come back device->host
+             host->device, the step is planned (SharedCacheAttention.prepare), run, the output rows
+             come back device->host and every write block grows by its token
   roofline   compulsory KV bytes / measured duration of the streaming kernel, against the measured
              HBM copy bandwidth of this pool's B200s
-  cpu_baseline  the CPU oracle (port of the reference path) timed on this box's host cores
+  cpu_baseline  the CPU oracle (port of the reference path) timed on this box's host cores; its
+             output rows are also what the replayed step's rows are compared with (parity_checked)
+  side       (1 GPU) the other configurations, briefly: view prefill, GDN decode step, GDN chunked
+             prefill, block merge -- each with its own roofline and CPU baseline
 With ``--impl reference`` the CPU oracle alone is timed on the same workload (rank 0 only).
+``--workload prefill|gdn_step|gdn_prefill|block_merge`` prints one of the side lines alone.
 """
 
 from __future__ import annotations
@@ -44,9 +50,14 @@ SHARED_LEN = 8192
 PRIVATE_LEN = 2048
 PAGE_SIZE = 16
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel over its algorithmic bytes in the
-# committed ncu capture (269.4 MB read + 7.1 MB of split-K partials written for 268.6 MB of K/V)
-NCU_TRAFFIC_RATIO = 276.5 / 268.6
+FALLBACK_TFLOPS = 1590.0
+MIN_TIMED_MS = 100.0        # the rounds of the headline measurement cover at least this long
+MIN_ROUNDS = 50
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernels of the default step, from the
+# committed ncu summary profiles/view_decode_config2_step_traffic.md (same command as this bench with
+# --kernel-only).  Only valid for the default workload; any other size reports traffic null.
+NCU_STEP_TRAFFIC = {"view_decode_stream_kernel": 269_845_000, "view_dense_tc_kernel": 17_441_000}
+SIDE_WORKLOADS = ("prefill", "gdn_step", "gdn_prefill", "block_merge")
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -59,17 +70,18 @@ def workload_config(n_gpus: int) -> dict:
         "l2": "inputs larger than L2 (285 MB of KV per step vs 126 MB L2)",
         "step": "store_kv + view_decode (streaming pass || dense tiles of the shared block, merge), "
                 "plan resident, replayed from a CUDA graph",
-        "e2e_step": "H2D q/k/v + prepare() + forward() + D2H out, one layer",
+        "e2e_step": "H2D q/k/v + plan_writes + prepare() + forward() + D2H out + append_token, one layer",
     }
 
 
-def measured_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def load_peaks() -> dict:
     try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm": float(p["hbm_gbs"]), "tflops": float(p["bf16_tflops"]),
+                "tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "kind": "measured"}
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+        return {"hbm": FALLBACK_HBM_GBS, "tflops": FALLBACK_TFLOPS, "tflops_sustained": 1400.0, "kind": "fallback"}
 
 
 class ClockSampler:
@@ -123,26 +135,31 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_step_seconds(case, repeats: int):
-    """Time the CPU oracle on one full step (store + attention over all views)."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
+# ------------------------------------------------------------------------------------------------
+# CPU legs (the only places that run oracle/)
+def cpu_decode_step(case, repeats: int):
+    """Time the CPU oracle on one full step (store + attention over all views); returns the median
+    seconds and the step's output rows."""
     from oracle import view_oracle as vo
 
     pending, slots, positions = case.plan_writes()
     Hkv, D = case.num_kv_heads, case.head_dim
-    times = []
+    times, out = [], None
     for _ in range(repeats + 1):
         k_pool, v_pool = case.k_pool, case.v_pool
         t0 = time.perf_counter()
         vo.store_kv(k_pool, v_pool, case.k_new.view(-1, Hkv, D), case.v_new.view(-1, Hkv, D),
                     positions.long(), slots.long(), case.cos_sin)
-        vo.view_decode(case.q, k_pool, v_pool, case.group, pending, slots.tolist(), case.cos_sin,
-                       case.num_q_heads)
+        out = vo.view_decode(case.q, k_pool, v_pool, case.group, pending, slots.tolist(), case.cos_sin,
+                             case.num_q_heads)
         times.append(time.perf_counter() - t0)
-    return statistics.median(times[1:] or times)   # the first pass also warms the caches
+    return statistics.median(times[1:] or times), out   # the first pass also warms the caches
 
 
 def run_reference(args, rank: int) -> None:
+    """The reference arm: the CPU port of the path on all host cores, same workload and metric.
+    The host processes one 64-request shard per step whatever ``--gpus`` says: its throughput does
+    not depend on how many GPUs the other arm uses."""
     if rank != 0:
         return
     import benchcases as wl
@@ -150,25 +167,37 @@ def run_reference(args, rank: int) -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     case = wl.config2_decode(page_size=PAGE_SIZE, requests=REQUESTS, shared_len=SHARED_LEN,
                              private_len=PRIVATE_LEN)
-    for _ in range(max(0, min(args.warmup, 1))):
-        cpu_step_seconds(case, 0)
-    steps = max(1, min(args.steps, 5))
-    sec = cpu_step_seconds(case, steps)
+    t0 = time.perf_counter()
+    cpu_decode_step(case, 0)
+    est = time.perf_counter() - t0
+    # the run stays within a few minutes: fewer steps only if the host is far slower than expected
+    budget = 150.0
+    warmup = max(1, min(args.warmup, int(budget * 0.2 / est) or 1))
+    steps = max(1, min(args.steps, int(budget * 0.8 / est) or 1))
+    for _ in range(warmup - 1):            # the sizing pass above was the first warm-up step
+        cpu_decode_step(case, 0)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_decode_step(case, 0)
+        times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
     value = REQUESTS / sec
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": workload_config(1),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
-                         "kind": "port",
-                         "sample": f"full step: 64 requests, {steps} timed repeats (median), torch CPU fp32"},
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"one 64-request shard per step, {steps} timed steps (mean), torch CPU fp32; "
+                                   "the host's throughput does not grow with the number of GPUs"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
 def time_graph(fn, iters: int, device) -> float:
     """Milliseconds per call of ``fn`` replayed from a CUDA graph (events on the replay stream)."""
     side = torch.cuda.Stream(device=device)
@@ -203,150 +232,244 @@ def time_plain(fn, iters: int) -> float:
     return e0.elapsed_time(e1) / iters
 
 
-def run_side_workload(args, device) -> None:
-    """Other rows of the scope table, one JSON line each (not the headline metric):
-    view prefill (config 3), GDN decode step (config 4b), GDN prefill scan (config 4a)."""
+def timed_cpu(fn, repeats: int = 1) -> float:
+    """Median wall seconds of ``fn`` after one warm-up call."""
+    fn()
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times)
+
+
+# ------------------------------------------------------------------------------------------------
+# Side workloads: the other rows of the scope table
+def side_prefill(device, iters, peaks, with_cpu, requests=16):
+    """Config 3: batched view-conditioned prefill (tensor bound)."""
     import benchcases as wl
 
-    peaks = {}
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            peaks = json.load(f)
-    except Exception:
-        pass
-    hbm = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
-    tflops = float(peaks.get("bf16_tflops", 1590.0))
-    iters = max(3, min(args.steps, 20))
-    if args.workload == "prefill":
-        case = wl.config3_prefill(requests=args.requests if args.requests != REQUESTS else 16)
-        dp = wl.DevicePrefill(case, device)
-        batch = dp.plan()
-        ms = time_graph(lambda: dp.forward(batch), iters, device)
-        dp.attn.check_status()
-        achieved = case.flops() / ms / 1e9
-        line = {"metric": "view_prefill_tflops", "value": achieved, "unit": "TFLOP/s", "ms_per_step": ms,
-                "config": {"workload": "config3 view-conditioned prefill: 16 requests x 512 new tokens, 2-6 context "
-                                       "blocks of 1K-8K tokens, Hq32/Hkv8/D128, page 16", "engine": dp.attn.dense_engine},
-                "roofline": {"bound": "tensor", "achieved": achieved, "peak": tflops, "unit": "TFLOP/s",
-                             "frac": achieved / tflops, "traffic": None, "algorithmic_flops": case.flops()}}
-    elif args.workload == "block_merge":
-        from async_llm_b200 import BlockOps, MHAKVCache, PageAllocator, SharedCacheAttention
+    case = wl.config3_prefill(requests=requests)
+    dp = wl.DevicePrefill(case, device)
+    batch = dp.plan()
+    ms = time_graph(lambda: dp.forward(batch), iters, device)
+    dp.attn.check_status()
+    achieved = case.flops() / ms / 1e9
+    rows = sum(r["num_new"] for r in case.requests)
+    res = {"metric": "view_prefill_tflops", "value": achieved, "unit": "TFLOP/s", "ms": ms,
+           "tokens_per_s": rows / (ms * 1e-3),
+           "config": {"workload": f"config3 view-conditioned prefill: {requests} requests x 512 new tokens, 2-6 "
+                                  "context blocks of 1K-8K tokens, Hq32/Hkv8/D128, page 16, one layer",
+                      "engine": dp.attn.dense_engine},
+           "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                        "frac": achieved / peaks["tflops"], "peak_kind": f"{peaks['kind']} burst (kernel timed alone)",
+                        "frac_of_sustained": achieved / peaks["tflops_sustained"], "traffic": None,
+                        "algorithmic_flops": case.flops()}}
+    if with_cpu:
+        from oracle import view_oracle as vo
 
-        layers, Hkv, D, P, T = 24, 2, 256, PAGE_SIZE, 8192
-        pages = 4 * T // P + 8
-        pool = MHAKVCache(Hkv, layers, D, pages, P, torch.bfloat16, device)
-        pool._buf.normal_()
-        attn = SharedCacheAttention(pool, wl.cos_sin_table(D, 32768, 1e7).to(device), 16, Hkv, D, P,
-                                    torch.bfloat16, device)
-        alloc = PageAllocator(pages, P, device)
-        ops = BlockOps(pool, alloc, attn, P, device)
-        left, right = ops.create_block(), ops.create_block()
-        for b in (left, right):
-            b.page_starts = alloc.alloc_pages(T // P).tolist()
-            b.num_tokens = T
-        src = torch.cat((left.token_slots_tensor(), right.token_slots_tensor()))
-        dst = (alloc.alloc_pages(2 * T // P).to(torch.int32).unsqueeze(1)
-               + torch.arange(P, dtype=torch.int32, device=device)).reshape(-1)
-        alloc.free_pages(dst[::P].contiguous())
-        kern_ms = time_graph(lambda: ops._copy_slots(src, dst, T, T), iters, device)
-
-        def merge_and_free():
-            ops.free_block(ops.merge_blocks(left, right))
-
-        ms = time_plain(merge_and_free, iters)
-        attn.check_status()
-
-        def eager_copy():   # the reference's per-layer gather / scatter, without its key rotation
-            s64, d64 = src.long(), dst.long()
-            for i in range(layers):
-                for cache in (pool.k_cache(i), pool.v_cache(i)):
-                    flat = cache.reshape(-1, Hkv, D)
-                    flat.index_copy_(0, d64, flat.index_select(0, s64))
-
-        eager_ms = time_plain(eager_copy, max(2, iters // 4))
-        algo = 2 * T * layers * 2 * Hkv * D * 2 * 2      # tokens x layers x (K, V) rows, read + write
-        achieved = algo / kern_ms / 1e6
-        line = {"metric": "block_merge_gbs", "value": achieved, "unit": "GB/s", "ms_per_step": kern_ms,
-                "config": {"workload": "merge of two 8192-token blocks into a fresh block: 24 layers, Hkv2/D256, page 16, "
-                                       "right-hand keys rotated by 8192 positions; value = the copy kernel alone",
-                           "merge_blocks_ms": ms, "torch_eager_copy_only_ms": eager_ms},
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                             "frac": achieved / hbm, "traffic": None, "algorithmic_bytes": algo}}
-    else:
-        from async_llm_b200.blocks import CacheBlock
-        from async_llm_b200.view_gdn import SharedCacheGDN
-
-        Hk, Hv, dk, dv = 16, 32, 128, 128
-        ar = SharedCacheGDN(num_heads=Hv, head_k_dim=dk, head_v_dim=dv, conv_dim=2 * Hk * dk + Hv * dv,
-                            conv_kernel=4, device=device, num_k_heads=Hk)
-        if args.workload == "gdn_step":
-            W = 128
-            shared = CacheBlock(device, PAGE_SIZE)
-            shared.linear_affine[0] = wl.gdn_random_summary(Hv, dk, dv, 1, device)
-            privs = []
-            for w in range(W):
-                b = CacheBlock(device, PAGE_SIZE)
-                b.linear_affine[0] = wl.gdn_random_summary(Hv, dk, dv, 10 + w, device)
-                privs.append(b)
-            ar.set_context([[shared, b] for b in privs], privs)
-            ar.prepare_decode(1, torch.bfloat16)
-            q, k, v, g, beta = (t.to(device) for t in wl.gdn_tokens(W, Hk, Hv, dk, dv, 4000))
-            ms = time_graph(lambda: ar.decode_step(0, q, k, v, g, beta), iters, device)
-            ar.finish_decode(False)
-            algo = W * Hv * (dk * dk + dv * dk) * 4 * 2   # read + write of the write block's A_hat, B_hat
-            achieved = algo / ms / 1e6
-            line = {"metric": "gdn_step_gbs", "value": achieved, "unit": "GB/s", "ms_per_step": ms,
-                    "config": {"workload": "config4b GDN decode step: 128 workers, chain [shared, private], Hk16/Hv32, "
-                                           "dk=dv=128, fp32 summaries, one layer"},
-                    "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                                 "frac": achieved / hbm, "traffic": None, "algorithmic_bytes": algo}}
-        else:
-            R, T, NB = 8, 2048, 4
-            toks = [tuple(t.to(device) for t in wl.gdn_tokens(R * T, Hk, Hv, dk, dv, 4100 + j)) for j in range(NB)]
-
-            def four_blocks():
-                # every request writes NB blocks in order; block j starts from the fold of blocks < j
-                written = [[] for _ in range(R)]
-                for j in range(NB):
-                    new = [CacheBlock(device, PAGE_SIZE) for _ in range(R)]
-                    ar.set_context([written[r] + [new[r]] for r in range(R)], new, prefill_segments=[T] * R)
-                    ar.prepare_prefill(1, torch.bfloat16, R * T)
-                    ar.prefill_scan(0, *toks[j])
-                    ar.finish_prefill(True)
-                    for r in range(R):
-                        written[r].append(new[r])
-
-            ms = time_plain(four_blocks, max(2, iters // 4))
-            tokens = R * T * NB
-            chunked = ar.prefill_engine == "chunk"
-            # per token, head and part: scan 3 x 128 x 128 x 2 flops; chunk: the UT-transform products
-            # (K K^T, Q K^T, W, U, W X, Q X, P Vnew, K^T Vnew) of _chunk_gated_delta_rule
-            chunk_flops = 2.0 * (64 * 64 * 128 * 4 + 64 * 128 * 128 * 3 + 64 * 64 * 128) * 3 / 64
-            scan_flops = 3 * 2.0 * 128 * 128 * 3
-            tensor_peak = tflops
-            achieved_tf = tokens * Hv * (chunk_flops if chunked else scan_flops) / ms / 1e9
-            line = {"metric": "gdn_prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
-                    "ms_per_step": ms,
-                    "config": {"workload": "config4a GDN prefill: 8 requests x 4 blocks of 2048 tokens written in order "
-                                           "(block j starts from the fold of the earlier blocks' summaries), "
-                                           "Hk16/Hv32, dk=dv=128, one layer; joint [S | A_hat | B_hat] pass; host "
-                                           "planning between the blocks is inside the timed region",
-                               "engine": ar.prefill_engine},
-                    "roofline": {"bound": "tensor" if chunked else "fp32 fma", "achieved": achieved_tf, "unit": "TFLOP/s",
-                                 "peak": tensor_peak if chunked else None,
-                                 "frac": achieved_tf / tensor_peak if chunked else None, "traffic": None}}
-    line.update({"n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-                 "side_workload": args.workload})
-    print(json.dumps(line), flush=True)
+        one = wl.config3_prefill(requests=1)
+        Hkv, D = one.num_kv_heads, one.head_dim
+        k_pool, v_pool = one.k_pool.clone(), one.v_pool.clone()
+        vo.store_kv(k_pool, v_pool, one.k_new.view(-1, Hkv, D), one.v_new.view(-1, Hkv, D),
+                    one.positions.long(), one.out_loc.long(), one.cos_sin)
+        sec = timed_cpu(lambda: vo.view_prefill(one.q, k_pool, v_pool, one.specs(), one.cos_sin, one.num_q_heads))
+        res["cpu_baseline"] = {"value": one.flops() / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                               "kind": "port", "sample": "the first of the 16 requests (512 new tokens), one timed pass"}
+    return res
 
 
+def side_block_merge(device, iters, peaks, with_cpu):
+    """Block merge: copy of two 8192-token blocks into a fresh block, right-hand keys re-rotated."""
+    import benchcases as wl
+    from async_llm_b200 import BlockOps, MHAKVCache, PageAllocator, SharedCacheAttention
+
+    layers, Hkv, D, P, T = 24, 2, 256, PAGE_SIZE, 8192
+    pages = 4 * T // P + 8
+    pool = MHAKVCache(Hkv, layers, D, pages, P, torch.bfloat16, device)
+    pool._buf.normal_()
+    attn = SharedCacheAttention(pool, wl.cos_sin_table(D, 32768, 1e7).to(device), 16, Hkv, D, P,
+                                torch.bfloat16, device)
+    alloc = PageAllocator(pages, P, device)
+    ops = BlockOps(pool, alloc, attn, P, device)
+    left, right = ops.create_block(), ops.create_block()
+    for b in (left, right):
+        b.page_starts = alloc.alloc_pages(T // P).tolist()
+        b.num_tokens = T
+    src = torch.cat((left.token_slots_tensor(), right.token_slots_tensor()))
+    dst = (alloc.alloc_pages(2 * T // P).to(torch.int32).unsqueeze(1)
+           + torch.arange(P, dtype=torch.int32, device=device)).reshape(-1)
+    alloc.free_pages(dst[::P].contiguous())
+    kern_ms = time_graph(lambda: ops._copy_slots(src, dst, T, T), iters, device)
+
+    def merge_and_free():
+        ops.free_block(ops.merge_blocks(left, right))
+
+    ms = time_plain(merge_and_free, max(2, iters // 2))
+    attn.check_status()
+    algo = 2 * T * layers * 2 * Hkv * D * 2 * 2      # tokens x layers x (K, V) rows, read + write
+    achieved = algo / kern_ms / 1e6
+    res = {"metric": "block_merge_gbs", "value": achieved, "unit": "GB/s", "ms": kern_ms,
+           "config": {"workload": "merge of two 8192-token blocks into a fresh block: 24 layers, Hkv2/D256, page 16, "
+                                  "right-hand keys rotated by 8192 positions; value = the copy kernel alone",
+                      "merge_blocks_ms": ms},
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                        "frac": achieved / peaks["hbm"], "peak_kind": peaks["kind"], "traffic": None,
+                        "algorithmic_bytes": algo}}
+    if with_cpu:
+        # the reference's per-layer gather / scatter (session.py:489-528) on the K rows of two layers
+        kc = torch.randn(2, pages * P, Hkv, D).to(torch.bfloat16)
+        s64, d64 = src.cpu().long(), dst.cpu().long()
+
+        def two_layers():
+            for layer in range(2):
+                kc[layer].index_copy_(0, d64, kc[layer].index_select(0, s64))
+
+        sec = timed_cpu(two_layers, 3)
+        res["cpu_baseline"] = {"value": 2 * (2 * T) * Hkv * D * 2 * 2 / sec / 1e9, "unit": "GB/s",
+                               "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": "K rows of 2 of the 24 layers, index_select + index_copy_, no rotation"}
+    del pool
+    return res
+
+
+def _gdn_object(device):
+    from async_llm_b200.view_gdn import SharedCacheGDN
+
+    Hk, Hv, dk, dv = 16, 32, 128, 128
+    ar = SharedCacheGDN(num_heads=Hv, head_k_dim=dk, head_v_dim=dv, conv_dim=2 * Hk * dk + Hv * dv,
+                        conv_kernel=4, device=device, num_k_heads=Hk)
+    return ar, Hk, Hv, dk, dv
+
+
+def side_gdn_step(device, iters, peaks, with_cpu):
+    """Config 4b: fused GDN decode step, 128 workers, chain [shared, private] (HBM bound)."""
+    import benchcases as wl
+    from async_llm_b200.blocks import CacheBlock
+
+    ar, Hk, Hv, dk, dv = _gdn_object(device)
+    W = 128
+    shared = CacheBlock(device, PAGE_SIZE)
+    shared.linear_affine[0] = wl.gdn_random_summary(Hv, dk, dv, 1, device)
+    privs = []
+    for w in range(W):
+        b = CacheBlock(device, PAGE_SIZE)
+        b.linear_affine[0] = wl.gdn_random_summary(Hv, dk, dv, 10 + w, device)
+        privs.append(b)
+    chains = [[shared, b] for b in privs]
+    ar.set_context(chains, privs)
+    ar.prepare_decode(1, torch.bfloat16)
+    toks = wl.gdn_tokens(W, Hk, Hv, dk, dv, 4000)
+    q, k, v, g, beta = (t.to(device) for t in toks)
+    ms = time_graph(lambda: ar.decode_step(0, q, k, v, g, beta), iters, device)
+    ar.finish_decode(False)
+    algo = W * Hv * (dk * dk + dv * dk) * 4 * 2   # read + write of the write block's A_hat, B_hat
+    achieved = algo / ms / 1e6
+    res = {"metric": "gdn_step_gbs", "value": achieved, "unit": "GB/s", "ms": ms, "tokens_per_s": W / (ms * 1e-3),
+           "config": {"workload": "config4b GDN decode step: 128 workers, chain [shared, private], Hk16/Hv32, "
+                                  "dk=dv=128, fp32 summaries, one layer"},
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                        "frac": achieved / peaks["hbm"], "peak_kind": peaks["kind"], "traffic": None,
+                        "algorithmic_bytes": algo}}
+    if with_cpu:
+        from oracle import gdn_oracle as go
+
+        n = 16   # workers of the sample
+        pairs = lambda b: (b.linear_affine[0][0].cpu(), b.linear_affine[0][1].cpu())
+        cq, ck, cv, cg, cb = (t[:n] for t in toks)
+        rep = lambda x: x.repeat_interleave(Hv // Hk, dim=1)
+        chains_cpu = [[pairs(shared), pairs(privs[w])] for w in range(n)]
+        targets_cpu = [pairs(privs[w]) for w in range(n)]
+        sec = timed_cpu(lambda: go.decode_step(chains_cpu, targets_cpu, rep(cq), rep(ck), cv, cg, cb))
+        res["cpu_baseline"] = {"value": algo * n / W / sec / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(),
+                               "kind": "port", "tokens_per_s": n / sec,
+                               "sample": "16 of the 128 workers: compose + one recurrent token + summary update"}
+    return res
+
+
+def side_gdn_prefill(device, iters, peaks, with_cpu):
+    """Config 4a: chunked GDN prefill, 8 requests x 4 blocks of 2048 tokens written in order."""
+    import benchcases as wl
+    from async_llm_b200.blocks import CacheBlock
+
+    ar, Hk, Hv, dk, dv = _gdn_object(device)
+    R, T, NB = 8, 2048, 4
+    toks = [tuple(t.to(device) for t in wl.gdn_tokens(R * T, Hk, Hv, dk, dv, 4100 + j)) for j in range(NB)]
+
+    def four_blocks():
+        # every request writes NB blocks in order; block j starts from the fold of blocks < j
+        written = [[] for _ in range(R)]
+        for j in range(NB):
+            new = [CacheBlock(device, PAGE_SIZE) for _ in range(R)]
+            ar.set_context([written[r] + [new[r]] for r in range(R)], new, prefill_segments=[T] * R)
+            ar.prepare_prefill(1, torch.bfloat16, R * T)
+            ar.prefill_scan(0, *toks[j])
+            ar.finish_prefill(True)
+            for r in range(R):
+                written[r].append(new[r])
+
+    ms = time_plain(four_blocks, max(2, iters // 4))
+    tokens = R * T * NB
+    chunked = ar.prefill_engine == "chunk"
+    # Per 64-token chunk and value head.  Pre-pass, computed ONCE for the three parts of the joint
+    # state [S | A_hat | B_hat]: K K^T and Q K^T (64x64x128 each), W = T K' and U = T V' (64x128x64
+    # each) plus the triangular inverse.  State pass, once per PART: W X (64x128x128) and
+    # K^T Vnew (128x128x64); Q X (64x128x128) and P Vnew (64x128x64) for part 0 only.
+    mm = lambda m, n, k: 2.0 * m * n * k
+    pre = 2 * mm(64, 64, 128) + 2 * mm(64, 128, 64) + mm(64, 64, 64)
+    state = 3 * (mm(64, 128, 128) + mm(128, 128, 64)) + mm(64, 128, 128) + mm(64, 128, 64)
+    chunk_flops = (pre + state) / 64           # per token and head
+    scan_flops = 3 * 3 * 2.0 * 128 * 128       # three parts x (decay, k^T S, rank-1) per token and head
+    flops = tokens * Hv * (chunk_flops if chunked else scan_flops)
+    achieved_tf = flops / ms / 1e9
+    # q, k (16 heads), v, out (32 heads) bf16 per token + g, beta fp32: read once, out written once;
+    # the scratch of the pre-pass (1.16 KB per token and head, written then read by three parts) and
+    # the summaries come on top of this compulsory figure
+    algo_bytes = tokens * ((2 * Hk * dk + 2 * Hv * dv) * 2 + 2 * Hv * 4)
+    res = {"metric": "gdn_prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms": ms,
+           "config": {"workload": "config4a GDN prefill: 8 requests x 4 blocks of 2048 tokens written in order "
+                                  "(block j starts from the fold of the earlier blocks' summaries), Hk16/Hv32, "
+                                  "dk=dv=128, one layer; joint [S | A_hat | B_hat] pass; host planning between the "
+                                  "blocks is inside the timed region", "engine": ar.prefill_engine},
+           "roofline": {"bound": "tensor" if chunked else "fp32 fma", "achieved": achieved_tf, "unit": "TFLOP/s",
+                        "peak": peaks["tflops"] if chunked else None,
+                        "frac": achieved_tf / peaks["tflops"] if chunked else None, "peak_kind": peaks["kind"],
+                        "algorithmic_flops": flops, "traffic": None,
+                        "bytes": {"algorithmic_bytes": algo_bytes, "achieved_gbs": algo_bytes / ms / 1e6,
+                                  "frac_of_hbm": algo_bytes / ms / 1e6 / peaks["hbm"]},
+                        "note": "a chain of 32 dependent chunks per (block, request, head): neither bound is approached"}}
+    if with_cpu:
+        from oracle import gdn_oracle as go
+
+        cq, ck, cv, cg, cb = (t[:T].cpu() for t in toks[0])
+        rep = lambda x: x.repeat_interleave(Hv // Hk, dim=1)
+        sec = timed_cpu(lambda: go.chunk_delta_rule(rep(cq)[None], rep(ck)[None], cv[None], cg[None], cb[None]))
+        res["cpu_baseline"] = {"value": T / sec, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": "one request x one 2048-token block, the S scan only (no summary parts)"}
+    return res
+
+
+SIDE_FUNCS = {"prefill": side_prefill, "gdn_step": side_gdn_step, "gdn_prefill": side_gdn_prefill,
+              "block_merge": side_block_merge}
+
+
+def run_side(name, device, iters, peaks, with_cpu) -> dict:
+    torch.set_num_threads(os.cpu_count() or 1)
+    res = SIDE_FUNCS[name](device, iters, peaks, with_cpu)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="skip the side workloads of the default 1-GPU run")
     # smaller cases of the same kernels for profiler captures (not a bench line)
     ap.add_argument("--requests", type=int, default=REQUESTS)
     ap.add_argument("--shared-len", type=int, default=SHARED_LEN)
@@ -355,10 +478,11 @@ def main() -> None:
     ap.add_argument("--hkv", type=int, default=2)
     ap.add_argument("--head-dim", type=int, default=256)
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE)
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn_step", "gdn_prefill", "block_merge"],
-                    help="decode = the headline metric; the others print one extra JSON line each")
+    ap.add_argument("--workload", default="decode", choices=["decode", *SIDE_WORKLOADS],
+                    help="decode = the headline metric (with the side workloads embedded); the others "
+                         "print that side line alone")
     ap.add_argument("--kernel-only", action="store_true",
-                    help="run warmup+steps decode steps and exit (for ncu captures)")
+                    help="run warmup+steps steps of the workload and exit (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -382,10 +506,22 @@ def main() -> None:
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+    peaks = load_peaks()
+    default_workload = (args.requests, args.shared_len, args.private_len, args.hq, args.hkv, args.head_dim,
+                        args.page_size) == (REQUESTS, SHARED_LEN, PRIVATE_LEN, 16, 2, 256, PAGE_SIZE)
 
     if args.workload != "decode":
         if rank == 0:
-            run_side_workload(args, device)
+            if args.kernel_only:
+                # a few launches of the side workload's kernels, nothing else (profiler captures)
+                run_side(args.workload, device, max(3, args.steps), peaks, False)
+                print(json.dumps({"kernel_only": True, "workload": args.workload}))
+            else:
+                line = run_side(args.workload, device, max(3, min(args.steps, 20)), peaks, not args.no_cpu_baseline)
+                line["ms_per_step"] = line["ms"]
+                line.update({"n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                             "side_workload": args.workload})
+                print(json.dumps(line), flush=True)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -403,14 +539,18 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    K, Wm = args.steps, args.warmup
+    e2e_steps = min(max(K, 20), 50)
+    # pages the end-to-end steps consume: every write block grows by one token per step
+    e2e_pages = args.requests * (-(-(2 * e2e_steps + 8) // args.page_size) + 1)
+    n_shared = -(-args.shared_len // args.page_size) + 8 if world > 1 else 0
     # every rank holds its own shard of requests; the shared block is replicated per GPU
-    spare = -(-args.shared_len // args.page_size) + 8 if world > 1 else 0
     case = wl.config2_decode(page_size=args.page_size, seed=2000 + rank, requests=args.requests,
                              shared_len=args.shared_len, private_len=args.private_len,
                              num_q_heads=args.hq, num_kv_heads=args.hkv, head_dim=args.head_dim,
-                             spare_pages=spare)
+                             spare_pages=e2e_pages + n_shared)
     dv = wl.DeviceView(case, device)
-    replicated_bytes = 0
+    publish = {"bytes": 0, "ms": None}
     if world > 1:
         # the shared block is written on rank 0 and published once into every other GPU's own
         # pool pages (NCCL broadcast over NVLink); decode steps then run without any collective
@@ -418,19 +558,24 @@ def main() -> None:
         from async_llm_b200.sharding import BlockReplicator
 
         alloc = PageAllocator(0, args.page_size, device)
-        alloc._free = torch.tensor(case.free_pages[len(case.writes):], dtype=torch.int32, device=device)
-        case.free_pages = case.free_pages[: len(case.writes)]
+        alloc._free = torch.tensor(case.free_pages[-n_shared:], dtype=torch.int32, device=device)
+        case.free_pages = case.free_pages[:-n_shared]
         rep = BlockReplicator(dv.pool, alloc)
         shared = case.blocks["shared"] if rank == 0 else CacheBlock(torch.device("cpu"), args.page_size)
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
         rep.publish(shared, src=0)
-        torch.cuda.synchronize()
+        p1.record()
+        barrier()
         case.blocks["shared"] = shared
         t = torch.tensor([rep.bytes_sent], dtype=torch.int64, device=device)
         dist.all_reduce(t)
-        replicated_bytes = int(t.item())
+        publish = {"bytes": int(t.item()), "ms": max_over_ranks(p0.elapsed_time(p1)),
+                   "note": "one-time broadcast of the shared block's rows of every layer into each receiver's own "
+                           "pages (host bookkeeping included); outside the timed steps"}
     batch = dv.plan()
     plan = batch.attn_metadata.plan
-    K, Wm = args.steps, args.warmup
     if args.kernel_only:
         for _ in range(Wm + K):
             dv.decode(batch)
@@ -455,22 +600,37 @@ def main() -> None:
             graph_out = dv.decode(batch)
     for _ in range(Wm):
         step_graph.replay()
-    barrier()
+    torch.cuda.synchronize()
+    # one untimed round sizes the measurement: rounds of exactly K replays until >= MIN_TIMED_MS
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        step_graph.replay()
+    e1.record()
+    e1.synchronize()
+    est_round_ms = max_over_ranks(e0.elapsed_time(e1))
+    rounds = int(max(MIN_ROUNDS, -(-MIN_TIMED_MS // max(est_round_ms, 1e-3))))
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(rounds)]
+    barrier()
     with ClockSampler(local_rank) as clocks:
-        e0.record()
-        for _ in range(K):
-            step_graph.replay()
-        e1.record()
+        t_wall = time.perf_counter()
+        for a, b in events:
+            a.record()
+            for _ in range(K):
+                step_graph.replay()
+            b.record()
         barrier()
+        timed_wall_ms = (time.perf_counter() - t_wall) * 1e3
         # keep the sampler alive for a few samples even when the region is short
-        t_end = time.time() + 0.6
+        t_end = time.time() + 0.5
         while time.time() < t_end:
             step_graph.replay()
         torch.cuda.synchronize()
-    ms_step = max_over_ranks(e0.elapsed_time(e1) / K)
+    per_step = sorted(a.elapsed_time(b) / K for a, b in events)
+    ms_step = max_over_ranks(statistics.median(per_step))
+    ms_step_min = max_over_ranks(per_step[0])
     dv.attn.check_status()
-    del graph_out
+    gpu_rows = graph_out.float().cpu()
 
     # ---- the dominant kernel alone (streaming pass), for the roofline: one launch captured in
     # a graph, replayed back to back between two events on the launching stream
@@ -480,35 +640,56 @@ def main() -> None:
 
     pool = pool_struct(dv.pool, 0, case.num_q_heads, dv.attn._cos_sin, dv.attn.rotary_dim)
     out = torch.empty(args.requests, case.num_q_heads * case.head_dim, dtype=torch.bfloat16, device=device)
-    plan.struct.phase_mask = 2 | 4  # skip merge and dense tiles: the streaming pass only
-    kern_graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(kern_graph, stream=side):
-            rc = _lib.lib().va_view_decode(C.byref(pool), C.byref(plan.struct), dv.q.data_ptr(),
-                                           dv.q.stride(0), out.data_ptr(), out.stride(0),
-                                           dv.attn._partial_o.data_ptr(), dv.attn._partial_ml.data_ptr(),
-                                           dv.attn.status().data_ptr(), _lib.stream_ptr())
-    _lib.check(rc, "va_view_decode")
-    plan.struct.phase_mask = 0
-    for _ in range(3):
-        kern_graph.replay()
-    torch.cuda.synchronize()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n_kern = max(10, min(K, 100))
-    k0.record()
-    for _ in range(n_kern):
-        kern_graph.replay()
-    k1.record()
-    k1.synchronize()
-    kern_avg_ms = k0.elapsed_time(k1) / n_kern
+
+    def phase_ms(mask: int, iters: int) -> float:
+        plan.struct.phase_mask = mask
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                rc = _lib.lib().va_view_decode(C.byref(pool), C.byref(plan.struct), dv.q.data_ptr(),
+                                               dv.q.stride(0), out.data_ptr(), out.stride(0),
+                                               dv.attn._partial_o.data_ptr(), dv.attn._partial_ml.data_ptr(),
+                                               dv.attn.status().data_ptr(), _lib.stream_ptr())
+        plan.struct.phase_mask = 0
+        _lib.check(rc, "va_view_decode")
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(iters):
+            g.replay()
+        k1.record()
+        k1.synchronize()
+        return k0.elapsed_time(k1) / iters
+
+    n_kern = 200
+    kern_avg_ms = phase_ms(2 | 4, n_kern)                 # streaming pass only
+    dense_ms = phase_ms(1 | 2, n_kern) if plan.groups is not None else None   # shared-block tiles only
     # bytes the streaming kernel itself must read: the (row, kv head) key ranges in its items
     stream_keys = int(plan.host["items"][:, 2].sum()) if plan.num_items else 0
     algo_bytes = stream_keys * 2 * case.head_dim * 2
     step_bytes = case.kv_bytes_compulsory()
-    peak, peak_kind = measured_peak()
     achieved = algo_bytes / (kern_avg_ms * 1e-3) / 1e9
 
-    # ---- end to end through the public API with host buffers
+    # ---- CPU baseline of the same step, and the parity check of the replayed rows against it
+    cpu_baseline, parity = None, {"parity_checked": False}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        sec, want = cpu_decode_step(case, 3)
+        cpu_baseline = {"value": args.requests / sec, "unit": UNIT, "cores": torch.get_num_threads(),
+                        "kind": "port",
+                        "sample": f"full step: {args.requests} requests, 3 timed repeats (median), torch CPU fp32"}
+        diff = (gpu_rows - want.float()).abs()
+        parity = {"parity_checked": True, "parity_max_abs": float(diff.max()), "parity_mean_abs": float(diff.mean()),
+                  "parity_ok": bool(diff.max() <= 2e-2 and diff.mean() <= 1e-3),
+                  "parity_note": "rows of the graph-replayed step vs the CPU oracle's rows of the same step; "
+                                 "bounds 2e-2 max-abs, 1e-3 mean-abs"}
+        if not parity["parity_ok"]:
+            raise SystemExit(f"bench: the replayed step does not match the oracle: {parity}")
+    del graph_out
+
+    # ---- end to end through the public API with host buffers; every step appends its token
     q_h, k_h, v_h = (t.cpu().pin_memory() for t in (case.q, case.k_new, case.v_new))
     out_h = torch.empty(args.requests, case.num_q_heads * case.head_dim, dtype=torch.bfloat16).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in (q_h, k_h, v_h))
@@ -516,6 +697,18 @@ def main() -> None:
     from types import SimpleNamespace
 
     group = case.group   # the serving engine keeps its worker group between steps
+    targets = [case.blocks[n] for n in case.writes]
+    snapshot = [(b, b.num_tokens, list(b.page_starts)) for b in targets], list(case.free_pages)
+
+    def advance(pending):
+        """Book-keeping after a step: every write block now holds its new token."""
+        used = 0
+        for b in targets:
+            page = pending[id(b)]
+            b.append_token(page)
+            used += page is not None
+        if used:
+            del case.free_pages[:used]
 
     def e2e_step():
         pending, slots, positions = case.plan_writes()
@@ -528,27 +721,29 @@ def main() -> None:
         o = dv.attn.forward(qd, kd, vd, 0, b)
         out_h.copy_(o, non_blocking=True)
         torch.cuda.synchronize()
+        advance(pending)
+        return meta
 
-    e2e_steps = min(K, 50)
     for _ in range(3):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        e2e_step()
+        meta = e2e_step()
     barrier()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) / e2e_steps * 1e3)
+    plan_bytes = meta.plan.host_blob.numel() * 4 + 2 * args.requests * 4
 
     # The same work with the host planning of step n+1 issued while the GPU runs step n (the plan
     # depends on block lengths, not on the sampled tokens): every step still copies its inputs in,
-    # plans, runs and copies its result out; only the wait for the result moves behind the next
-    # step's planning.  Reported beside the strict number, not instead of it.
+    # plans, runs, copies its result out and appends; only the wait for the result moves behind the
+    # next step's planning.  Reported beside the strict number, not instead of it.
     def plan_step():
         pending, slots, positions = case.plan_writes()
-        return dv.attn.prepare(group, pending, slots), positions, slots
+        return dv.attn.prepare(group, pending, slots), positions, slots, pending
 
     def launch_step(planned):
-        meta, positions, slots = planned
+        meta, positions, slots, _ = planned
         qd = q_h.to(device, non_blocking=True)
         kd = k_h.to(device, non_blocking=True)
         vd = v_h.to(device, non_blocking=True)
@@ -556,56 +751,73 @@ def main() -> None:
                             out_loc=slots.to(device, non_blocking=True), mrope_positions=None)
         out_h.copy_(dv.attn.forward(qd, kd, vd, 0, b), non_blocking=True)
 
-    planned = plan_step()
-    for _ in range(3):
-        launch_step(planned)
+    def pipelined(n):
         planned = plan_step()
-        torch.cuda.synchronize()
+        for _ in range(n):
+            launch_step(planned)
+            advance(planned[3])          # the lengths after this step are known before its result is
+            planned = plan_step()
+            torch.cuda.synchronize()
+
+    pipelined(3)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        launch_step(planned)
-        planned = plan_step()
-        torch.cuda.synchronize()
+    pipelined(e2e_steps)
     barrier()
     e2e_pipelined_ms = max_over_ranks((time.perf_counter() - t0) / e2e_steps * 1e3)
-    h2d += plan.host_blob.numel() * 4 + 2 * args.requests * 4
-
-    cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        torch.set_num_threads(os.cpu_count() or 1)
-        sec = cpu_step_seconds(case, 3)
-        cpu_baseline = {"value": args.requests / sec, "unit": UNIT, "cores": torch.get_num_threads(),
-                        "kind": "port",
-                        "sample": "full step: 64 requests, 3 timed repeats (median), torch CPU fp32"}
+    dv.attn.check_status()
+    for b, n, pages in snapshot[0]:       # leave the case as it was
+        b.num_tokens, b.page_starts = n, pages
+    case.free_pages = snapshot[1]
 
     if rank == 0:
+        launches_per_step = 4 if plan.groups is not None else 3
+        stream_traffic = NCU_STEP_TRAFFIC["view_decode_stream_kernel"] if default_workload else None
         line = {
             "metric": METRIC, "value": args.requests * world / (ms_step * 1e-3), "unit": UNIT,
             "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": dict(workload_config(world), replicated_bytes_at_publish=replicated_bytes),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": int(algo_bytes * NCU_TRAFFIC_RATIO),
-                         "traffic_note": "dram read+write of one ncu capture of this kernel on the same private "
-                                         "blocks (276.5 MB for 268.6 MB of keys and values), scaled by the bytes "
-                                         "streamed",
-                         "peak_kind": peak_kind,
+            "data": "synthetic", "config": workload_config(world),
+            "timing": {"rounds": rounds, "steps_per_round": K, "ms_per_step_median": ms_step,
+                       "ms_per_step_min": ms_step_min, "timed_region_ms": timed_wall_ms,
+                       "note": "every round is exactly --steps graph replays between two CUDA events; median round, "
+                               "max over ranks"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm"], "traffic": stream_traffic,
+                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel "
+                                         "variant inside the step (ncu summary in profiles/)",
+                         "peak_kind": peaks["kind"],
                          "kernel": f"view_decode_stream_kernel<{args.head_dim}>", "kernel_ms": kern_avg_ms,
                          "algorithmic_bytes": algo_bytes,
                          "stream_sms": plan.struct.num_lanes // (4 if args.head_dim == 256 else 6),
+                         "dense_tiles_ms": dense_ms,
+                         "dense_tiles_traffic": NCU_STEP_TRAFFIC["view_dense_tc_kernel"] if default_workload else None,
                          "step_compulsory_bytes": step_bytes,
-                         "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak},
+                         "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm"]},
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": args.requests * world / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d + plan_bytes, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "steps": e2e_steps,
                     "pipelined_value": args.requests * world / (e2e_pipelined_ms * 1e-3),
                     "pipelined_note": "host planning of step n+1 overlapped with the GPU work of step n"},
-            "gpu_launches": (4 if plan.groups is not None else 3) * K,
+            "gpu_launches": launches_per_step * K * rounds,
             "clocks": clocks.summary(),
+            "publish": publish,
         }
+        line.update(parity)
+        if world == 1 and not args.no_side:
+            del dv
+            torch.cuda.empty_cache()
+            sides = {}
+            for name in SIDE_WORKLOADS:
+                try:
+                    sides[name] = run_side(name, device, 10, peaks, not args.no_cpu_baseline)
+                except Exception as exc:   # noqa: BLE001 -- a side line never costs the headline
+                    sides[name] = {"error": f"{type(exc).__name__}: {exc}"}
+            line["side"] = sides
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

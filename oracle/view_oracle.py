@@ -330,3 +330,34 @@ def view_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, sp
         out[offset: offset + S] = torch.einsum("shgl,lhd->shgd", p, v).reshape(S, num_q_heads, D)
         offset += S
     return out.view(N, -1)
+
+
+def plain_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, slot_rows: Sequence[Sequence[int]],
+                    extend_lens: Sequence[int], num_q_heads: int, sm_scale: Optional[float] = None) -> torch.Tensor:
+    """Causal paged attention of ordinary (view-less) batches: what the reference's stock backends
+    compute (minisgl/attention/fi.py:176-188, FlashInfer paged prefill with ``causal=True`` /
+    paged decode over ``page_table[table_idx, :device_len]``, page size 1).
+
+    Request ``r`` has keys at token slots ``slot_rows[r]`` (all already in the pool, the new ones
+    last) and ``extend_lens[r]`` query rows; query row ``i`` sees keys ``0 .. len - extend + i``.
+    ``q [rows, Hq*D]`` is used as given (the layer rotated it).  Returns fp32 ``[rows, Hq*D]``.
+    """
+    Hkv, D = k_pool.shape[-2], k_pool.shape[-1]
+    scale = D ** -0.5 if sm_scale is None else sm_scale
+    g = num_q_heads // Hkv
+    kf, vf = k_pool.reshape(-1, Hkv, D).float(), v_pool.reshape(-1, Hkv, D).float()
+    rows = sum(int(e) for e in extend_lens)
+    qh = q.reshape(rows, num_q_heads, D).float()
+    out = torch.zeros(rows, num_q_heads, D)
+    off = 0
+    for slots, S in zip(slot_rows, extend_lens):
+        S = int(S)
+        idx = torch.as_tensor(list(slots), dtype=torch.long)
+        L = idx.numel()
+        K, V = kf[idx], vf[idx]
+        s_ = torch.einsum("shgd,lhd->shgl", qh[off: off + S].view(S, Hkv, g, D), K) * scale
+        visible = torch.arange(L)[None, :] <= (L - S + torch.arange(S))[:, None]
+        s_ = s_.masked_fill(~visible[:, None, None, :], float("-inf"))
+        out[off: off + S] = torch.einsum("shgl,lhd->shgd", torch.softmax(s_, dim=-1), V).reshape(S, num_q_heads, D)
+        off += S
+    return out.view(rows, -1)
