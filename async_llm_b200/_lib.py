@@ -157,6 +157,7 @@ class VaGdnPrefillConv(C.Structure):
     _fields_ = [
         ("qkv", C.c_void_p), ("qkv_row_stride", C.c_int64), ("prior_conv", C.c_void_p),
         ("conv_weight", C.c_void_p), ("seg_off", C.c_void_p), ("qkv_out", C.c_void_p), ("conv_out", C.c_void_p),
+        ("prior_conv_ptrs", C.c_void_p), ("conv_out_ptrs", C.c_void_p),
         ("num_requests", C.c_int32), ("num_tokens", C.c_int32), ("conv_dim", C.c_int32), ("conv_kernel", C.c_int32),
     ]
 

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256) gdn_decode_pre_kernel(const __grid_consta
       if (t < K) {
         const float prod = __fmul_rn(__bfloat162float(win[t]), __bfloat162float(p.conv_weight[c * K + t]));
         total = __fadd_rn(total, prod);
-        out_w[c * K + t] = win[t];
+        if (out_w != nullptr) out_w[c * K + t] = win[t];   // null: a padding row of a fixed-capacity batch
       }
     }
     p.qkv_out[ch] = __float2bfloat16_rn(silu_f32(total));
@@ -123,6 +123,8 @@ struct PrefillConvParams {
   const int32_t* seg_off;            // [R + 1] token offsets of the requests
   __nv_bfloat16* qkv_out;            // [T, conv_dim]
   __nv_bfloat16* conv_out;           // [R, conv_dim, k]
+  const int64_t* prior_conv_ptrs;    // [R] addresses of [conv_dim, k] states (0 = zeros), or null
+  const int64_t* conv_out_ptrs;      // [R] addresses of the states to write (0 = skip), or null
   int32_t num_requests, num_tokens, conv_dim, conv_kernel;
 };
 
@@ -146,10 +148,16 @@ __global__ void __launch_bounds__(256) gdn_prefill_conv_kernel(const __grid_cons
   if (t < begin || t >= end) return;   // a token outside every segment (malformed offsets) is left alone
   const int K = p.conv_kernel;
   const int i = t - begin;             // index within the request
+  const int64_t r_off = static_cast<int64_t>(r) * p.conv_dim * K;
+  const __nv_bfloat16* prior_r =
+      p.prior_conv_ptrs != nullptr ? reinterpret_cast<const __nv_bfloat16*>(p.prior_conv_ptrs[r])
+                                   : (p.prior_conv != nullptr ? p.prior_conv + r_off : nullptr);
+  __nv_bfloat16* out_r = p.conv_out_ptrs != nullptr ? reinterpret_cast<__nv_bfloat16*>(p.conv_out_ptrs[r])
+                                                    : p.conv_out + r_off;
   auto input = [&](int idx, int c) -> __nv_bfloat16 {   // idx relative to the request's first token
     if (idx >= 0) return p.qkv[static_cast<int64_t>(begin + idx) * p.qkv_row_stride + c];
-    if (p.prior_conv == nullptr) return __float2bfloat16_rn(0.0f);
-    return p.prior_conv[(static_cast<int64_t>(r) * p.conv_dim + c) * K + (K + idx)];
+    if (prior_r == nullptr) return __float2bfloat16_rn(0.0f);
+    return prior_r[static_cast<int64_t>(c) * K + (K + idx)];
   };
   for (int c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
     float total = 0.0f;
@@ -162,10 +170,9 @@ __global__ void __launch_bounds__(256) gdn_prefill_conv_kernel(const __grid_cons
       }
     }
     p.qkv_out[static_cast<int64_t>(t) * p.conv_dim + c] = __float2bfloat16_rn(silu_f32(total));
-    if (t == end - 1) {
+    if (t == end - 1 && out_r != nullptr) {
       const int L = end - begin;
-      for (int j = 0; j < K; ++j)
-        p.conv_out[(static_cast<int64_t>(r) * p.conv_dim + c) * K + j] = input(L - K + j, c);
+      for (int j = 0; j < K; ++j) out_r[static_cast<int64_t>(c) * K + j] = input(L - K + j, c);
     }
   }
 }
@@ -225,9 +232,12 @@ extern "C" int va_gdn_prefill_conv(const VaGdnPrefillConv* a, va_stream_t stream
   if (a == nullptr || a->num_requests < 0 || a->num_tokens < 0 || a->conv_dim <= 0) return VA_ERR_BAD_ARG;
   if (a->conv_kernel < 1 || a->conv_kernel > kMaxConvKernel) return VA_ERR_UNSUPPORTED;
   if (a->num_tokens == 0 || a->num_requests == 0) return VA_OK;
-  if (!a->qkv || !a->conv_weight || !a->seg_off || !a->qkv_out || !a->conv_out) return VA_ERR_BAD_ARG;
+  if (!a->qkv || !a->conv_weight || !a->seg_off || !a->qkv_out || (!a->conv_out && !a->conv_out_ptrs))
+    return VA_ERR_BAD_ARG;
   if (a->qkv_row_stride < a->conv_dim) return VA_ERR_BAD_ARG;
   PrefillConvParams p;
+  p.prior_conv_ptrs = a->prior_conv_ptrs;
+  p.conv_out_ptrs = a->conv_out_ptrs;
   p.qkv = static_cast<const __nv_bfloat16*>(a->qkv);
   p.qkv_row_stride = a->qkv_row_stride;
   p.prior_conv = static_cast<const __nv_bfloat16*>(a->prior_conv);

@@ -124,3 +124,85 @@ def prefill_conv(qkv: torch.Tensor, prior_conv: Optional[torch.Tensor], conv_wei
     args.num_requests, args.num_tokens, args.conv_dim, args.conv_kernel = R, T, conv_dim, k
     _lib.check(_lib.lib().va_gdn_prefill_conv(C.byref(args), _lib.stream_ptr()), "va_gdn_prefill_conv")
     return qkv_out, conv_out
+
+
+class GatedDeltaNetLayer:
+    """One Gated DeltaNet layer over worker chains: the counterpart of the async-reasoning entry
+    points of ``Qwen3_5GatedDeltaNet`` (minisgl/models/qwen3_5_delta.py:349-490).
+
+    The projections stay plain GEMMs (``torch.nn.functional.linear`` on the weights given here);
+    everything between them runs on this package's kernels through the prepared ``SharedCacheGDN``
+    object (``ar``) of the forward:
+
+      decode   ``ar.decode_pre`` (conv window + SiLU + gates + next window, one launch)
+               -> ``ar.decode_step`` (chain fold + one recurrent token + summary update, one launch)
+               -> ``gated_rmsnorm``
+      prefill  ``ar.prefill_pre`` (causal conv of all requests + next windows, one launch), gates
+               -> ``ar.prefill_scan`` (chain fold, joint scan: outputs + the write blocks' summaries)
+               -> ``gated_rmsnorm``
+
+    The caller brackets a model forward with ``ar.set_context`` / ``ar.prepare_decode`` (or
+    ``prepare_prefill``) and ``ar.finish_decode(ok)`` (``finish_prefill``), exactly as the reference
+    session does (minisgl/shared_cache/session.py:1195-1227); new summaries and conv windows become
+    visible to the blocks only then.
+
+    Weights: ``w_qkv [2*Hk*dk + Hv*dv, hidden]``, ``w_z [Hv*dv, hidden]``, ``w_a``, ``w_b [Hv, hidden]``,
+    ``w_out [hidden, Hv*dv]`` bf16; ``conv_weight [conv_dim, 1, k]``; ``A_log``, ``dt_bias [Hv]``;
+    ``norm_weight [dv]``.
+    """
+
+    def __init__(self, lin_idx: int, num_k_heads: int, num_v_heads: int, head_k_dim: int, head_v_dim: int,
+                 w_qkv: torch.Tensor, w_z: torch.Tensor, w_a: torch.Tensor, w_b: torch.Tensor, w_out: torch.Tensor,
+                 conv_weight: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, norm_weight: torch.Tensor,
+                 eps: float = 1e-6) -> None:
+        self.lin_idx = lin_idx
+        self.num_k_heads, self.num_v_heads = num_k_heads, num_v_heads
+        self.head_k_dim, self.head_v_dim = head_k_dim, head_v_dim
+        self.key_dim, self.value_dim = num_k_heads * head_k_dim, num_v_heads * head_v_dim
+        self.conv_dim = 2 * self.key_dim + self.value_dim
+        self.w_qkv, self.w_z, self.w_a, self.w_b, self.w_out = w_qkv, w_z, w_a, w_b, w_out
+        # one GEMM for the four input projections: rows [qkv | z | a | b]
+        self.w_in = torch.cat((w_qkv, w_z, w_a, w_b), dim=0).contiguous()
+        self.conv_weight = conv_weight.reshape(self.conv_dim, -1).to(torch.bfloat16).contiguous()
+        self.A_log = A_log.to(device=w_qkv.device, dtype=torch.float32).contiguous()
+        self.dt_bias = dt_bias.to(device=w_qkv.device, dtype=torch.float32).contiguous()
+        self.norm_weight = norm_weight.to(device=w_qkv.device, dtype=torch.float32).contiguous()
+        self.eps = float(eps)
+
+    def _project(self, x: torch.Tensor):
+        y = torch.nn.functional.linear(x, self.w_in)
+        return torch.split(y, [self.conv_dim, self.value_dim, self.num_v_heads, self.num_v_heads], dim=-1)
+
+    def _split_heads(self, qkv: torch.Tensor):
+        n = qkv.shape[0]
+        q, k, v = torch.split(qkv, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        return (q.reshape(n, self.num_k_heads, self.head_k_dim), k.reshape(n, self.num_k_heads, self.head_k_dim),
+                v.reshape(n, self.num_v_heads, self.head_v_dim))
+
+    def _finish(self, core: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
+        n = core.shape[0]
+        normed = gated_rmsnorm(core.reshape(n, self.num_v_heads, self.head_v_dim),
+                               z.reshape(n, self.num_v_heads, self.head_v_dim), self.norm_weight, self.eps)
+        return torch.nn.functional.linear(normed.reshape(n, self.value_dim), self.w_out)
+
+    def forward_ar_decode(self, x: torch.Tensor, ar) -> torch.Tensor:
+        """``x [W, hidden]``: one token per worker (``_forward_ar_decode``, qwen3_5_delta.py:443-490)."""
+        qkv, z, a, b = self._project(x)
+        qkv2, beta, g = ar.decode_pre(self.lin_idx, qkv, self.conv_weight, a, b, self.A_log, self.dt_bias)
+        q, k, v = self._split_heads(qkv2)
+        core = ar.decode_step(self.lin_idx, q, k, v, g, beta)
+        return self._finish(core, z)
+
+    def forward_ar_prefill(self, x: torch.Tensor, ar) -> torch.Tensor:
+        """``x [N, hidden]``: the rows of all requests of a batched prefill, request-major
+        (``_forward_ar_prefill``, qwen3_5_delta.py:349-441)."""
+        qkv, z, a, b = self._project(x)
+        qkv2 = ar.prefill_pre(self.lin_idx, qkv, self.conv_weight)
+        q, k, v = self._split_heads(qkv2)
+        beta = b.sigmoid()                                                     # _gates, :296-299
+        g = -self.A_log.exp() * torch.nn.functional.softplus(a.float() + self.dt_bias)
+        core = ar.prefill_scan(self.lin_idx, q, k, v, g, beta)
+        return self._finish(core, z)
+
+
+__all__ = ["decode_conv_gates", "gated_rmsnorm", "prefill_conv", "GatedDeltaNetLayer"]

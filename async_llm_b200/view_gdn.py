@@ -35,6 +35,100 @@ from .blocks import CacheBlock
 GDN_ENGINES = {"scan": 0, "chunk": 1}   # VA_GDN_ENGINE_* of the C header
 
 
+# rows of the per-step address table [8, layers, workers, depth]
+ROW_CHAIN_A, ROW_CHAIN_B, ROW_READ_A, ROW_READ_B, ROW_CONV_READ, ROW_WRITE_A, ROW_WRITE_B, ROW_CONV_WRITE = range(8)
+
+
+class GDNDecodeBuffers:
+    """Fixed-capacity, address-stable address tables of a GDN decode step, for CUDA-graph replay.
+
+    The counterpart of the reference's class of the same name (minisgl/shared_cache/gdn_decode.py:62-214):
+    one capacity -- ``layers`` linear layers, ``workers`` rows, chains of at most ``depth`` blocks --
+    whose device tables never move.  ``SharedCacheGDN.prepare_decode(..., buffers=self)`` plans on the
+    host and copies the step's addresses INTO these tables; the kernels of ``decode_pre`` /
+    ``decode_step`` are always launched over ``workers`` rows with the same arguments, so a graph
+    captured once keeps working while topology and block summaries change behind it.  Rows beyond
+    the planned batch carry zero addresses: they read the identity, write nothing and their output
+    rows are ignored.  New summaries still go to FRESH slabs allocated on the host at prepare time
+    (never inside a capture), so readers of the previous summary are never disturbed
+    (gdn_decode.py:112-121).  Exceeding a capacity raises ``ValueError`` before anything is copied.
+    """
+
+    def __init__(self, ar: "SharedCacheGDN", layers: int, workers: int, depth: int, dtype: torch.dtype):
+        self.ar, self.layers, self.workers, self.depth, self.dtype = ar, int(layers), int(workers), max(1, int(depth)), dtype
+        self.device = ar.device
+        on_gpu = self.device.type == "cuda"
+        shape = (8, self.layers, self.workers, self.depth)
+        self.host_tab = torch.zeros(shape, dtype=torch.int64, pin_memory=on_gpu)
+        self.host_rw = torch.zeros(self.layers, 6, self.workers, dtype=torch.int64, pin_memory=on_gpu)
+        self.tab = self.host_tab.to(self.device) if on_gpu else self.host_tab
+        self.rw = self.host_rw.to(self.device) if on_gpu else self.host_rw
+        self.event = torch.cuda.Event() if on_gpu else None
+        self.prepare_count = 0
+
+    @property
+    def write_ptrs(self) -> torch.Tensor:
+        """``[layers, 3, workers]`` view of the output addresses (A_hat, B_hat, conv window); zeroing it
+        turns a replay into a step that publishes nothing (gdn_decode.py: ``write_ptrs``)."""
+        return self.rw[:, 3:6]
+
+    def retire_completed(self) -> None:
+        self.ar._retire()
+
+    def load(self, tab: np.ndarray) -> None:
+        """Copy a step's table ``[8, layers, W, depth]`` (W, depth within capacity) into the fixed tables."""
+        _, layers, W, depth = tab.shape
+        if layers != self.layers:
+            raise ValueError(f"GDN buffers were prepared for {self.layers} layers, not {layers}")
+        if W > self.workers:
+            raise ValueError(f"GDN batch of {W} workers exceeds the prepared capacity {self.workers}")
+        if depth > self.depth:
+            raise ValueError(f"GDN chain depth {depth} exceeds the prepared capacity {self.depth}")
+        if self.event is not None:
+            self.event.synchronize()   # the previous upload has left the staging buffers
+        hv = self.host_tab.numpy()
+        hv[...] = 0
+        hv[:, :, :W, :depth] = tab
+        self.host_rw.numpy()[...] = hv[2:8, :, :, 0].transpose(1, 0, 2)
+        if self.tab is not self.host_tab:
+            self.tab.copy_(self.host_tab, non_blocking=True)
+            self.rw.copy_(self.host_rw, non_blocking=True)
+            self.event.record()
+        self.prepare_count += 1
+
+
+class GDNPrefillBuffers(GDNDecodeBuffers):
+    """Fixed-capacity tables of a batched GDN prefill (minisgl/shared_cache/gdn_prefill.py:11-61):
+    on top of the decode tables, ``rows`` token rows at most, the requests' row offsets at a fixed
+    device address and the chunk engine's scratch reserved for ``rows`` tokens.  Requests beyond the
+    planned batch are empty ranges."""
+
+    def __init__(self, ar: "SharedCacheGDN", layers: int, workers: int, depth: int, dtype: torch.dtype, rows: int):
+        super().__init__(ar, layers, workers, depth, dtype)
+        self.rows = int(rows)
+        on_gpu = self.device.type == "cuda"
+        self.host_seg = torch.zeros(self.workers + 1, dtype=torch.int32, pin_memory=on_gpu)
+        self.seg = self.host_seg.to(self.device) if on_gpu else self.host_seg
+        self.scratch = None
+        if on_gpu:
+            need = int(_lib.lib().va_gdn_prefill_scratch_bytes(self.rows, ar.num_heads))
+            self.scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
+
+    def check_segments(self, segments: Sequence[int]) -> None:
+        if len(segments) > self.workers or any(int(t) <= 0 for t in segments) or sum(segments) > self.rows:
+            raise ValueError("Prefill exceeds prepared request/token capacity")
+
+    def load_segments(self, segments: Sequence[int]) -> None:
+        self.check_segments(segments)
+        off = np.zeros(self.workers + 1, np.int32)
+        off[1: len(segments) + 1] = np.cumsum(np.asarray(segments, np.int64))
+        off[len(segments) + 1:] = off[len(segments)]
+        self.host_seg.numpy()[...] = off
+        if self.seg is not self.host_seg:
+            self.seg.copy_(self.host_seg, non_blocking=True)
+            self.event.record()
+
+
 class SharedCacheGDN:
     """Per-forward composer / capturer of GDN block summaries over worker chains."""
 
@@ -61,6 +155,9 @@ class SharedCacheGDN:
         if self.prefill_engine not in GDN_ENGINES:
             raise ValueError(f"prefill_engine must be one of {sorted(GDN_ENGINES)}")
         self._chunk_scratch: Optional[torch.Tensor] = None
+        self._init_row_index: Optional[torch.Tensor] = None
+        self.decode_buffers: Optional[GDNDecodeBuffers] = None
+        self.prefill_buffers: Optional[GDNPrefillBuffers] = None
         self.device = torch.device(device)
         self.state_dtype = state_dtype
         self.num_heads = num_heads              # value heads (post GQA repeat)
@@ -145,13 +242,17 @@ class SharedCacheGDN:
         keep.append(c[3])
         return c[2][:layers]
 
-    def _build_tables(self, layers: int, with_outputs: bool):
-        """Pointer tables of every layer in one upload: chain [L, W, depth], read/write [L, W]."""
+    def _build_tables(self, layers: int, with_outputs: bool, buffers: Optional[GDNDecodeBuffers] = None):
+        """Address tables of every layer in one upload: ``[8, L, W, depth]`` (rows ``ROW_*``); the read /
+        write rows use ``[..., 0]`` only.  With ``buffers`` the tables are copied into its fixed device
+        tensors and the step runs over its ``workers`` rows."""
         chains, targets = self.cache_structure, self.write_to
         if len(chains) != len(targets) or len({id(t) for t in targets}) != len(targets):
             raise ValueError("GDN forward needs one distinct write target per worker")
         W = len(chains)
         depth = max(1, max((len(c) for c in chains), default=0))
+        if buffers is not None and (W > buffers.workers or depth > buffers.depth or layers != buffers.layers):
+            buffers.load(np.zeros((8, layers, W, depth), np.int64))   # raises the capacity error
         keep: list = []
         # every distinct block once; row 0 of the address table stands for "no block here"
         index: Dict[int, int] = {}
@@ -174,12 +275,11 @@ class SharedCacheGDN:
                 chain_idx[w, j] = number(block)
             target_idx[w] = number(targets[w])
         addr = np.stack(rows)                                     # [blocks + 1, L, 2]
-        # chain_a, chain_b, then in [..., 0]: read_a/b, write_a/b, conv read / write
         tab = np.zeros((8, layers, W, depth), dtype=np.int64)
-        tab[0] = addr[chain_idx, :, 0].transpose(2, 0, 1)
-        tab[1] = addr[chain_idx, :, 1].transpose(2, 0, 1)
-        tab[2, :, :, 0] = addr[target_idx, :, 0].T
-        tab[3, :, :, 0] = addr[target_idx, :, 1].T
+        tab[ROW_CHAIN_A] = addr[chain_idx, :, 0].transpose(2, 0, 1)
+        tab[ROW_CHAIN_B] = addr[chain_idx, :, 1].transpose(2, 0, 1)
+        tab[ROW_READ_A, :, :, 0] = addr[target_idx, :, 0].T
+        tab[ROW_READ_B, :, :, 0] = addr[target_idx, :, 1].T
         out_a = out_b = conv_out = None
         if with_outputs:
             H, dk, dv = self.num_heads, self.head_k_dim, self.head_v_dim
@@ -189,12 +289,12 @@ class SharedCacheGDN:
             has = caddr != 0
             last = depth - 1 - np.argmax(has[:, ::-1, :], axis=1)        # [W, L]
             picked = np.take_along_axis(caddr, last[:, None, :], axis=1)[:, 0, :]
-            tab[6, :, :, 0] = np.where(has.any(axis=1), picked, 0).T
+            tab[ROW_CONV_READ, :, :, 0] = np.where(has.any(axis=1), picked, 0).T
             conv_out = [torch.empty(layers, self.conv_dim, self.conv_kernel, dtype=torch.bfloat16,
                                     device=self.device) for _ in targets]
             conv_stride = self.conv_dim * self.conv_kernel * 2
-            tab[7, :, :, 0] = (np.fromiter((t.data_ptr() for t in conv_out), np.int64, W)[None, :]
-                               + np.arange(layers, dtype=np.int64)[:, None] * conv_stride)
+            tab[ROW_CONV_WRITE, :, :, 0] = (np.fromiter((t.data_ptr() for t in conv_out), np.int64, W)[None, :]
+                                            + np.arange(layers, dtype=np.int64)[:, None] * conv_stride)
             # one all-layer allocation per worker: a stopped worker must not pin a whole batch
             steps = np.arange(layers, dtype=np.int64)
             if dk == dv:
@@ -204,26 +304,31 @@ class SharedCacheGDN:
                 out_b = None
                 base = np.fromiter((t.data_ptr() for t in out_a), np.int64, W)
                 stride = H * dk * dk * 4
-                tab[4, :, :, 0] = base[None, :] + steps[:, None] * stride
-                tab[5, :, :, 0] = base[None, :] + (layers + steps[:, None]) * stride
+                tab[ROW_WRITE_A, :, :, 0] = base[None, :] + steps[:, None] * stride
+                tab[ROW_WRITE_B, :, :, 0] = base[None, :] + (layers + steps[:, None]) * stride
             else:
                 out_a = [torch.empty(layers, 1, H, dk, dk, dtype=torch.float32, device=self.device) for _ in targets]
                 out_b = [torch.empty(layers, 1, H, dv, dk, dtype=torch.float32, device=self.device) for _ in targets]
-                tab[4, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_a), np.int64, W)[None, :]
-                                   + steps[:, None] * (out_a[0].stride(0) * 4))
-                tab[5, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_b), np.int64, W)[None, :]
-                                   + steps[:, None] * (out_b[0].stride(0) * 4))
-        on_gpu = self.device.type == "cuda"
-        host = torch.from_numpy(tab)
-        if on_gpu:
-            host = host.pin_memory()
-        dev = host.to(self.device, non_blocking=True)
-        keep.append(host)
-        # per-layer rows of the six [W] address lists (read_a/b, write_a/b, conv read/write), compact
-        rw = dev[2:8, :, :, 0].transpose(0, 1).contiguous()            # [L, 6, W]
-        return {"tab": dev, "rw": rw, "host": tab, "depth": depth, "W": W, "layers": layers, "out_a": out_a,
-                "out_b": out_b, "conv_out": conv_out, "conv_layers": set(), "keep": keep,
-                "targets": list(targets)}
+                tab[ROW_WRITE_A, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_a), np.int64, W)[None, :]
+                                             + steps[:, None] * (out_a[0].stride(0) * 4))
+                tab[ROW_WRITE_B, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_b), np.int64, W)[None, :]
+                                             + steps[:, None] * (out_b[0].stride(0) * 4))
+        if buffers is not None:
+            buffers.load(tab)
+            dev, rw, run_W, run_depth = buffers.tab, buffers.rw, buffers.workers, buffers.depth
+        else:
+            on_gpu = self.device.type == "cuda"
+            host = torch.from_numpy(tab)
+            if on_gpu:
+                host = host.pin_memory()
+            dev = host.to(self.device, non_blocking=True)
+            keep.append(host)
+            # per-layer rows of the six [W] address lists (read a/b/conv, write a/b/conv), compact
+            rw = dev[2:8, :, :, 0].transpose(0, 1).contiguous()            # [L, 6, W]
+            run_W, run_depth = W, depth
+        return {"tab": dev, "rw": rw, "host": tab, "depth": run_depth, "W": run_W, "real_W": W, "layers": layers,
+                "out_a": out_a, "out_b": out_b, "conv_out": conv_out, "conv_layers": set(),
+                "keep": keep, "targets": list(targets), "buffers": buffers}
 
     def _retire(self) -> None:
         self._pending = [(ev, refs) for ev, refs in self._pending if not ev.query()]
@@ -235,7 +340,8 @@ class SharedCacheGDN:
             raise RuntimeError("Previous GDN forward has not been published")
         if self.device.type == "cuda":
             self._retire()
-        self._step = self._build_tables(layers, with_outputs=True)
+        self._step = self._build_tables(layers, with_outputs=True, buffers=buffers)
+        self.decode_buffers = buffers
         self._prepared_decode = True
         self.prepare_count += 1
 
@@ -246,7 +352,7 @@ class SharedCacheGDN:
         if success:
             layers = st["layers"]
             # the new summaries' addresses are known without touching the tensors again: [W, L, 2]
-            new_ptrs = np.ascontiguousarray(st["host"][4:6, :, :, 0].transpose(2, 1, 0))
+            new_ptrs = np.ascontiguousarray(st["host"][ROW_WRITE_A:ROW_WRITE_B + 1, :, :, 0].transpose(2, 1, 0))
             for w, target in enumerate(st["targets"]):
                 if st["out_b"] is None:
                     slab_a = slab_b = st["out_a"][w]
@@ -265,7 +371,7 @@ class SharedCacheGDN:
                     target._gdn_ptr_cache = (target._gdn_revision, self.device, new_ptrs[w], [slab_a, slab_b])
                 if len(st["conv_layers"]) == layers and len(target.linear_conv_state) == layers:
                     target._gdn_conv_cache = (target._gdn_revision, self.device,
-                                              np.ascontiguousarray(st["host"][7, :, w, 0]), [st["conv_out"][w]])
+                                              np.ascontiguousarray(st["host"][ROW_CONV_WRITE, :, w, 0]), [st["conv_out"][w]])
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream(self.device))
@@ -300,7 +406,7 @@ class SharedCacheGDN:
         a.chain_a = tab[0, lin_idx].data_ptr()
         a.chain_b = tab[1, lin_idx].data_ptr()
         row = st["rw"].data_ptr() + lin_idx * 6 * W * 8                # [6, W] int64 rows of this layer
-        a.read_a, a.read_b, a.write_a, a.write_b = (row + i * W * 8 for i in range(4))
+        a.read_a, a.read_b, a.write_a, a.write_b = (row + i * W * 8 for i in (0, 1, 3, 4))
         a.num_workers, a.depth = W, st["depth"]
         a.num_k_heads, a.num_v_heads = q.shape[1], self.num_heads
         a.head_k_dim, a.head_v_dim = self.head_k_dim, self.head_v_dim
@@ -342,7 +448,7 @@ class SharedCacheGDN:
         args = _lib.VaGdnDecodePre()
         args.qkv, args.qkv_row_stride = qkv.data_ptr(), qkv.stride(0)
         args.prior_conv, args.conv_out = None, None
-        args.prior_conv_ptrs, args.conv_out_ptrs = row + 4 * W * 8, row + 5 * W * 8
+        args.prior_conv_ptrs, args.conv_out_ptrs = row + 2 * W * 8, row + 5 * W * 8
         args.conv_weight, args.a, args.b = weight.data_ptr(), a2.data_ptr(), b2.data_ptr()
         args.a_log, args.dt_bias = a_log.data_ptr(), bias.data_ptr()
         args.qkv_out, args.beta_out, args.beta_f32_out, args.g_out = (qkv_out.data_ptr(), beta16.data_ptr(),
@@ -425,8 +531,14 @@ class SharedCacheGDN:
             raise RuntimeError("Previous GDN forward has not been published")
         if self.device.type == "cuda":
             self._retire()
-        self._step = self._build_tables(layers, with_outputs=True)
-        self._step["segments"] = list(self.prefill_segments or [rows])
+        segments = list(self.prefill_segments or [rows])
+        if buffers is not None:
+            buffers.check_segments(segments)
+        self._step = self._build_tables(layers, with_outputs=True, buffers=buffers)
+        self._step["segments"] = segments
+        if buffers is not None:
+            buffers.load_segments(segments)
+        self.prefill_buffers = buffers
         self._prepared_prefill = True
         self.prepare_count += 1
 
@@ -435,16 +547,29 @@ class SharedCacheGDN:
             self._publish(success)
             self._prepared_prefill = False
 
+    def _init_rows(self) -> torch.Tensor:
+        """Rows (read a, read b, write a, write b) of a layer's ``[6, W]`` address list."""
+        if self._init_row_index is None:
+            self._init_row_index = torch.tensor([0, 1, 3, 4], dtype=torch.int64, device=self.device)
+        return self._init_row_index
+
     def _scan(self, q, k, v, g, beta, segments, state0, init, eps, want_out=True, keep=None,
-              final_state=None, engine="scan"):
+              final_state=None, engine="scan", buffers=None):
         if not q.is_cuda:
             raise RuntimeError("the GDN scan kernel needs CUDA tensors: there is no CPU fallback")
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         g32, b32 = g.float().contiguous(), beta.float().contiguous()
         N = q.shape[0]
         out = torch.empty(N, self.num_heads, self.head_v_dim, dtype=v.dtype, device=v.device)
-        seg = torch.tensor(np.concatenate(([0], np.cumsum(segments))), dtype=torch.int32)
-        seg_d = seg.to(self.device, non_blocking=True)
+        if buffers is not None:
+            # fixed capacity: the offsets sit at a fixed address, requests beyond the batch are empty
+            # ranges, rows beyond the last request are left alone
+            if N > buffers.rows:
+                raise ValueError(f"{N} token rows exceed the prepared capacity {buffers.rows}")
+            seg_d = buffers.seg
+        else:
+            seg = torch.tensor(np.concatenate(([0], np.cumsum(segments))), dtype=torch.int32)
+            seg_d = seg.to(self.device, non_blocking=True)
         init_t = init if isinstance(init, torch.Tensor) else torch.from_numpy(init).to(self.device)
         a = _lib.VaGdnPrefill()
         a.q, a.k, a.v, a.g, a.beta, a.out = (t.data_ptr() for t in (q, k, v, g32, b32, out))
@@ -452,14 +577,16 @@ class SharedCacheGDN:
         a.state0 = state0.data_ptr() if state0 is not None else None
         a.init_a, a.init_b, a.write_a, a.write_b = (init_t[i].data_ptr() for i in range(4))
         a.final_state = final_state.data_ptr() if final_state is not None else None
-        a.num_requests = len(segments)
+        a.num_requests = len(segments) if buffers is None else buffers.workers
         a.num_k_heads, a.num_v_heads = q.shape[1], self.num_heads
         a.head_k_dim, a.head_v_dim = self.head_k_dim, self.head_v_dim
         a.l2_eps, a.q_scale = eps, self.head_k_dim ** -0.5
         a.engine = GDN_ENGINES[engine]
         a.num_tokens = N
-        a.max_segment_tokens = int(max(segments)) if len(segments) else 0
-        if engine == "chunk" and N > 0:
+        a.max_segment_tokens = (int(max(segments)) if len(segments) else 0) if buffers is None else N
+        if engine == "chunk" and buffers is not None:
+            a.scratch, a.scratch_bytes = buffers.scratch.data_ptr(), buffers.scratch.numel()
+        elif engine == "chunk" and N > 0:
             # scratch of the chunk pre-pass (K, Q, -W, U, P rows per token and head), kept and grown
             need = int(_lib.lib().va_gdn_prefill_scratch_bytes(N, self.num_heads))
             if self._chunk_scratch is None or self._chunk_scratch.numel() < need:
@@ -469,6 +596,49 @@ class SharedCacheGDN:
         if keep is not None:
             keep += [q, k, v, g32, b32, seg_d, init_t]
         return out if want_out else None
+
+    def prefill_pre(self, lin_idx: int, qkv: torch.Tensor, conv_weight: torch.Tensor) -> torch.Tensor:
+        """Causal conv + SiLU of layer ``lin_idx`` over the prepared requests' rows, each request
+        preceded by its chain's most recent conv window, and the write blocks' next windows -- what
+        ``_forward_ar_prefill_one`` does request by request with ``prior_conv_states`` /
+        ``_prefill_conv_silu`` / ``set_conv_states`` (minisgl/models/qwen3_5_delta.py:399-437), and
+        ``GDNPrefillBuffers.convolve`` in the prepared path (minisgl/shared_cache/gdn_prefill.py:63-65).
+        ``qkv [N, conv_dim]`` bf16, rows request-major.  Returns ``qkv_conv [N, conv_dim]``; the new
+        windows become visible at ``finish_prefill(True)``."""
+        if not self._prepared_prefill:
+            raise RuntimeError("prefill_pre needs prepare_prefill first")
+        if not qkv.is_cuda:
+            raise RuntimeError("the GDN layer kernels need CUDA tensors: there is no CPU fallback")
+        st = self._step
+        W = st["W"]
+        N = qkv.shape[0]
+        assert qkv.shape[1] == self.conv_dim and qkv.dtype == torch.bfloat16
+        if qkv.stride(1) != 1:
+            qkv = qkv.contiguous()
+        weight = conv_weight.reshape(self.conv_dim, -1).to(torch.bfloat16).contiguous()
+        assert weight.shape[1] == self.conv_kernel
+        buffers = st["buffers"]
+        if buffers is not None:
+            seg_d = buffers.seg
+        else:
+            seg = torch.tensor(np.concatenate(([0], np.cumsum(st["segments"]))), dtype=torch.int32)
+            assert int(seg[-1]) == N, "prefill segments do not cover the batch"
+            seg_d = seg.to(self.device, non_blocking=True)
+        qkv_out = torch.empty(N, self.conv_dim, dtype=torch.bfloat16, device=self.device)
+        if buffers is not None:
+            qkv_out.zero_()    # rows beyond the planned batch are not written by the kernel
+        row = st["rw"].data_ptr() + lin_idx * 6 * W * 8
+        args = _lib.VaGdnPrefillConv()
+        args.qkv, args.qkv_row_stride = qkv.data_ptr(), qkv.stride(0)
+        args.prior_conv, args.conv_out = None, None
+        args.prior_conv_ptrs, args.conv_out_ptrs = row + 2 * W * 8, row + 5 * W * 8
+        args.conv_weight, args.seg_off = weight.data_ptr(), seg_d.data_ptr()
+        args.qkv_out = qkv_out.data_ptr()
+        args.num_requests, args.num_tokens, args.conv_dim, args.conv_kernel = W, N, self.conv_dim, self.conv_kernel
+        _lib.check(_lib.lib().va_gdn_prefill_conv(C.byref(args), _lib.stream_ptr()), "va_gdn_prefill_conv")
+        st["conv_layers"].add(lin_idx)
+        st["keep"] += [qkv, weight, seg_d]
+        return qkv_out
 
     def prefill_scan(self, lin_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                      g: torch.Tensor, beta: torch.Tensor, l2norm_eps: float = 1e-6,
@@ -484,16 +654,18 @@ class SharedCacheGDN:
             raise RuntimeError("prefill_scan needs prepare_prefill first")
         st = self._step
         state0 = None
-        if self.has_previous_affine(lin_idx):
+        # (a fixed-capacity step always composes: whether any chain carries a summary may change
+        # between replays; a chain without one composes to zeros)
+        if st["buffers"] is not None or self.has_previous_affine(lin_idx):
             state0 = torch.empty(st["W"], self.num_heads, self.head_k_dim, self.head_v_dim,
                                  dtype=torch.float32, device=self.device)
             rc = _lib.lib().va_gdn_compose(st["tab"][0, lin_idx].data_ptr(), st["tab"][1, lin_idx].data_ptr(),
                                            state0.data_ptr(), st["W"], st["depth"], self.num_heads,
                                            self.head_k_dim, self.head_v_dim, _lib.stream_ptr())
             _lib.check(rc, "va_gdn_compose")
-        init = st["tab"][2:6, lin_idx, :, 0].contiguous()
+        init = st["rw"][lin_idx].index_select(0, self._init_rows())    # read a/b, write a/b: [4, W]
         return self._scan(q, k, v, g, beta, st["segments"], state0, init, l2norm_eps, keep=st["keep"],
-                          final_state=final_state, engine=self.prefill_engine)
+                          final_state=final_state, engine=self.prefill_engine, buffers=st["buffers"])
 
 
-__all__ = ["SharedCacheGDN"]
+__all__ = ["SharedCacheGDN", "GDNDecodeBuffers", "GDNPrefillBuffers"]

@@ -456,7 +456,8 @@ int va_store_kv_mrope(const VaPool* pool, const void* k, int64_t k_row_stride, c
  *   beta_out   bf16 [W, Hv] sigmoid(b);  g_out fp32 [W, Hv] = -exp(a_log) * softplus(a + dt_bias)
  *   beta_f32_out  optional fp32 [W, Hv]: beta_out widened, the form va_gdn_step reads
  *   prior_conv_ptrs / conv_out_ptrs  optional device int64 [W]: the states as separate [conv_dim, k]
- *                 tensors named by address (0 = zeros for a prior state) instead of the dense arrays --
+ *                 tensors named by address (0 = zeros for a prior state, 0 = do not write the new
+ *                 state: a padding row of a fixed-capacity batch) instead of the dense arrays --
  *                 the blocks' own tensors, so that no gather / scatter launch is needed
  *                 (replaces gather_rows / scatter_rows of shared_cache/gdn_decode.py) */
 typedef struct VaGdnDecodePre {
@@ -495,8 +496,12 @@ int va_gdn_gated_rmsnorm(const void* x, const void* gate, const float* weight, v
  * state -- all requests of the batch in one launch.
  *   qkv       bf16 [T, conv_dim] rows of all requests, request r = rows seg_off[r] : seg_off[r+1]
  *   prior_conv bf16 [R, conv_dim, k] or NULL (zeros);  conv_weight bf16 [conv_dim, k]
- *   seg_off   device int32 [R + 1]
- *   qkv_out   bf16 [T, conv_dim];  conv_out bf16 [R, conv_dim, k] = last k of [prior | inputs] */
+ *   seg_off   device int32 [R + 1]; a request with an empty range is skipped, tokens beyond
+ *             seg_off[R] are left alone (padding of a fixed-capacity batch)
+ *   qkv_out   bf16 [T, conv_dim];  conv_out bf16 [R, conv_dim, k] = last k of [prior | inputs]
+ *   prior_conv_ptrs / conv_out_ptrs  optional device int64 [R]: the states as separate [conv_dim, k]
+ *             tensors named by address (0 = zeros for a prior state, 0 = do not write the new state)
+ *             instead of the dense arrays, as in VaGdnDecodePre */
 typedef struct VaGdnPrefillConv {
   const void* qkv;
   int64_t qkv_row_stride;
@@ -505,6 +510,8 @@ typedef struct VaGdnPrefillConv {
   const int32_t* seg_off;
   void* qkv_out;
   void* conv_out;
+  const int64_t* prior_conv_ptrs;
+  const int64_t* conv_out_ptrs;
   int32_t num_requests;
   int32_t num_tokens;
   int32_t conv_dim;

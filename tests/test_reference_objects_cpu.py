@@ -113,7 +113,7 @@ def test_prefill_planner_takes_reference_blocks(ref):
 
 def test_gdn_tables_take_reference_blocks(ref):
     from async_llm_b200.blocks import CacheBlock
-    from async_llm_b200.view_gdn import SharedCacheGDN
+    from async_llm_b200.view_gdn import ROW_CONV_READ, SharedCacheGDN
 
     shared_block, _, _ = ref
     H, dk, dv, conv_dim, kw = 2, 128, 128, 512, 4
@@ -139,7 +139,7 @@ def test_gdn_tables_take_reference_blocks(ref):
         ar.prepare_decode(2, torch.bfloat16)
         host = ar._step["host"]
         # addresses differ between the two builds; which entries are set must not
-        tabs.append((host[:4] != 0, host[6] != 0))
+        tabs.append((host[:4] != 0, host[ROW_CONV_READ] != 0))
         ar.finish_decode(True)
         for t in targets:
             assert set(t.linear_affine.keys()) == {0, 1}
