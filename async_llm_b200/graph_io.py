@@ -80,8 +80,12 @@ class _PrefillInputs:
 
 
 class SharedGraphIO:
-    def __init__(self, session, depth: int, prefill_rows: Sequence[int] = ()):
+    def __init__(self, session, depth: int, prefill_rows: Sequence[int] = (), *, dense_fraction: float = 0.0):
+        # dense_fraction: share of the SMs the captured decode launches reserve for the tensor-core
+        # tiles of blocks read by many workers (grid sizes are part of a captured graph, so the split
+        # between those tiles and the streaming lanes is frozen per profile)
         self.session, self.depth = session, int(depth)
+        self.dense_fraction = float(dense_fraction)
         self.attention: Dict[int, SharedDecodeAttentionBuffers] = {}
         self.gdn: Dict[int, GDNDecodeBuffers] = {}
         self.dummy_slots: Optional[torch.Tensor] = None
@@ -125,7 +129,8 @@ class SharedGraphIO:
         self.dummy_slots = s.page_allocator.alloc_pages(max(bs_list))
         for bs in bs_list:
             max_pages = bs * ((max_seq_len + P - 1) // P + self.depth)
-            self.attention[bs] = SharedDecodeAttentionBuffers(s.sc_attn, bs, self.depth, max_pages, self.dummy_slots[:bs])
+            self.attention[bs] = SharedDecodeAttentionBuffers(s.sc_attn, bs, self.depth, max_pages, self.dummy_slots[:bs],
+                                                              dense_fraction=self.dense_fraction)
             if s.sc_gdn is not None:
                 self.gdn[bs] = GDNDecodeBuffers(s.sc_gdn, self._linear_layers(), bs, self.depth, self._dtype())
         if self.prefill_rows:

@@ -327,7 +327,10 @@ class SharedCacheGDN:
             rw = dev[2:8, :, :, 0].transpose(0, 1).contiguous()            # [L, 6, W]
             run_W, run_depth = W, depth
         return {"tab": dev, "rw": rw, "host": tab, "depth": run_depth, "W": run_W, "real_W": W, "layers": layers,
-                "out_a": out_a, "out_b": out_b, "conv_out": conv_out, "conv_layers": set(),
+                "out_a": out_a, "out_b": out_b, "conv_out": conv_out,
+                # layers whose conv window this forward writes: recorded by decode_pre / prefill_pre as they
+                # run; a forward replayed from a graph runs no host code, so with fixed tables every layer counts
+                "conv_layers": set(range(layers)) if (buffers is not None and with_outputs) else set(),
                 "keep": keep, "targets": list(targets), "buffers": buffers}
 
     def _retire(self) -> None:

@@ -449,6 +449,144 @@ def side_gdn_prefill(device, iters, peaks, with_cpu):
     return res
 
 
+def run_hybrid(device, steps: int, warmup: int, peaks, rank: int, world: int, per_gpu: int = 32) -> dict:
+    """Config 5: the random-init hybrid decoder ([GDN, GDN, GDN, attention] x 8) decoding over cache
+    views, requests sharded over the GPUs.  Every rank takes part; returns the line on every rank
+    (rank 0 prints it).  A step = partition of the global request list, write planning, attention +
+    GDN planning into the captured tables, one replay of the captured forward, publish, append."""
+    import torch.distributed as dist
+
+    from async_llm_b200 import AsyncContext, CacheBlock
+    from async_llm_b200.sharding import BlockReplicator, partition_contexts
+    from hybrid_decoder import HybridConfig, HybridDecoder, HybridSession, synth_requests
+
+    cfg = HybridConfig()
+    P = cfg.page_size
+    spec = synth_requests(per_gpu * world, seed=5000)
+    shared_len = spec["shared_len"]
+    cpu = torch.device("cpu")
+    # host-only descriptors of every request of the job, for the partitioner (all ranks agree on them)
+    shared_desc = CacheBlock(cpu, P)
+    shared_desc.num_tokens = shared_len
+    descs = []
+    for lens in spec["private"]:
+        blocks = []
+        for n in lens:
+            b = CacheBlock(cpu, P)
+            b.num_tokens = n
+            blocks.append(b)
+        descs.append(AsyncContext(cache_view=[shared_desc] + blocks, output_block=blocks[-1]))
+    part = partition_contexts(descs, world)
+    sticky = {id(descs[i].output_block): g for g, shard in enumerate(part.shards) for i in shard}
+    mine = part.shards[rank]
+    max_workers = max(len(s) for s in part.shards)
+    total_steps = steps + warmup + 4
+    tokens_mine = sum(sum(spec["private"][i]) for i in mine)
+    pages = (shared_len + tokens_mine) // P + 4 * len(mine) + len(mine) * (total_steps // P + 2) + max_workers + 64
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_init = time.perf_counter()
+    model = HybridDecoder(cfg, device, seed=0)        # the same weights on every rank (replicated)
+    sess = HybridSession(model, pages, max_workers, depth=4, max_seq_len=shared_len + 3 * 4096 + total_steps,
+                         dense_fraction=0.25)
+    gen = torch.Generator(device=device).manual_seed(7000 + rank)
+    # the shared block is written on rank 0 and published once into every other GPU's own pages
+    publish = {"bytes": 0, "ms": None}
+    if world > 1:
+        shared = sess.new_block(shared_len, gen) if rank == 0 else CacheBlock(device, P)
+        rep = BlockReplicator(sess.kv_cache, sess.page_allocator)
+        barrier()
+        t0 = time.perf_counter()
+        rep.publish(shared, src=0, gdn_layers=range(cfg.num_linear_layers))
+        barrier()
+        t = torch.tensor([rep.bytes_sent], dtype=torch.int64, device=device)
+        dist.all_reduce(t)
+        publish = {"bytes": int(t.item()), "ms": max_over_ranks((time.perf_counter() - t0) * 1e3),
+                   "note": "shared 16K block: K/V rows of the 8 attention layers + summaries and conv windows of the "
+                           "24 GDN layers, broadcast once from rank 0 (NCCL), host bookkeeping included"}
+    else:
+        shared = sess.new_block(shared_len, gen)
+    contexts = {}
+    for i in mine:
+        blocks = [sess.new_block(n, gen) for n in spec["private"][i]]
+        contexts[i] = AsyncContext(cache_view=[shared] + blocks, output_block=blocks[-1])
+    sess.capture()
+    torch.cuda.synchronize()
+    init_s = time.perf_counter() - t_init
+
+    def step(k: int):
+        # the batch former: every rank deals the job's requests (pinned to the GPU holding their pages)
+        shards = partition_contexts(descs, world, sticky).shards[rank]
+        ctxs = [contexts[i] for i in shards]
+        sess.run_step(ctxs, [(11 * k + i) % cfg.vocab for i in shards])
+        for d in descs:
+            d.output_block.num_tokens += 1
+
+    for k in range(warmup):
+        step(k)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(device.index or 0) as clocks:
+        e0.record()
+        for k in range(steps):
+            step(warmup + k)
+        e1.record()
+        barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / steps)
+    sess.sc_attn.check_status()
+    # the captured forward alone (no host work between replays)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(5):
+        sess.graph.replay()
+    g1.record()
+    g1.synchronize()
+    graph_ms = max_over_ranks(g0.elapsed_time(g1) / 5)
+    # per-layer-type time of one eager forward (same kernels, launched one by one)
+    timers = {}
+    shards = partition_contexts(descs, world, sticky).shards[rank]
+    sess.forward_eager([contexts[i] for i in shards], [1] * len(shards), timers)
+    torch.cuda.synchronize()
+    by_type = {kind: sum(a.elapsed_time(b) for a, b in pairs) for kind, pairs in timers.items()}
+    # bytes one step must move on this GPU
+    kv_row = 2 * cfg.num_kv_heads * cfg.head_dim * 2
+    private_tokens = sum(sum(spec["private"][i]) for i in mine)
+    attn_bytes = cfg.num_attn_layers * (shared_len + private_tokens) * kv_row
+    gdn_bytes = cfg.num_linear_layers * len(mine) * cfg.gdn_v_heads * 2 * (cfg.gdn_head_dim ** 2) * 4 * 2
+    weight_bytes = cfg.param_bytes() - cfg.vocab * cfg.hidden * 2     # the embedding table is only indexed
+    step_bytes = weight_bytes + attn_bytes + gdn_bytes
+    n_req = per_gpu * world
+    return {"metric": "hybrid_decode_tokens_per_s", "value": n_req / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "ms": ms_step, "higher_is_better": True,
+            "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config5 hybrid decoder: 32 layers [GDN, GDN, GDN, attention] x 8, hidden 4096, attention "
+                                   "Hq16/Hkv4/D256 (gated, q/k norm), GDN Hk16/Hv32/128, SwiGLU 12288, vocab 151936, random "
+                                   f"bf16 weights replicated; {per_gpu} requests per GPU, views = shared 16384-token block + "
+                                   "1-3 private blocks of 512-4096 tokens, page 16",
+                       "global_requests": n_req, "requests_on_this_rank": len(mine), "captured_batch": max_workers,
+                       "parallelism": f"request-sharded x{world} by partition_contexts (sticky), no collective in a step"},
+            "graph_replay_ms": graph_ms, "host_ms_per_step": ms_step - graph_ms,
+            "eager_ms_by_layer_type": by_type,
+            "roofline": {"bound": "hbm", "achieved": step_bytes / graph_ms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": step_bytes / graph_ms / 1e6 / peaks["hbm"], "peak_kind": peaks["kind"], "traffic": None,
+                         "algorithmic_bytes": step_bytes,
+                         "bytes": {"weights": weight_bytes, "attention_kv": attn_bytes, "gdn_summaries": gdn_bytes},
+                         "note": "bytes one captured forward must move on this GPU / its replay time; the replicated "
+                                 "weight stream dominates at 32 requests per GPU"},
+            "publish": publish, "init_s": init_s, "clocks": clocks.summary()}
+
+
 SIDE_FUNCS = {"prefill": side_prefill, "gdn_step": side_gdn_step, "gdn_prefill": side_gdn_prefill,
               "block_merge": side_block_merge}
 
@@ -469,7 +607,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-side", action="store_true", help="skip the side workloads of the default 1-GPU run")
+    ap.add_argument("--no-side", action="store_true", help="skip the side workloads of the default run")
+    ap.add_argument("--no-hybrid", action="store_true", help="skip the full-model (config 5) side line")
     # smaller cases of the same kernels for profiler captures (not a bench line)
     ap.add_argument("--requests", type=int, default=REQUESTS)
     ap.add_argument("--shared-len", type=int, default=SHARED_LEN)
@@ -478,7 +617,7 @@ def main() -> None:
     ap.add_argument("--hkv", type=int, default=2)
     ap.add_argument("--head-dim", type=int, default=256)
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE)
-    ap.add_argument("--workload", default="decode", choices=["decode", *SIDE_WORKLOADS],
+    ap.add_argument("--workload", default="decode", choices=["decode", "hybrid", *SIDE_WORKLOADS],
                     help="decode = the headline metric (with the side workloads embedded); the others "
                          "print that side line alone")
     ap.add_argument("--kernel-only", action="store_true",
@@ -509,6 +648,15 @@ def main() -> None:
     peaks = load_peaks()
     default_workload = (args.requests, args.shared_len, args.private_len, args.hq, args.hkv, args.head_dim,
                         args.page_size) == (REQUESTS, SHARED_LEN, PRIVATE_LEN, 16, 2, 256, PAGE_SIZE)
+
+    if args.workload == "hybrid":
+        line = run_hybrid(device, max(3, args.steps), args.warmup, peaks, rank, world)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     if args.workload != "decode":
         if rank == 0:
@@ -805,15 +953,25 @@ def main() -> None:
             "publish": publish,
         }
         line.update(parity)
-        if world == 1 and not args.no_side:
-            del dv
-            torch.cuda.empty_cache()
-            sides = {}
-            for name in SIDE_WORKLOADS:
-                try:
-                    sides[name] = run_side(name, device, 10, peaks, not args.no_cpu_baseline)
-                except Exception as exc:   # noqa: BLE001 -- a side line never costs the headline
-                    sides[name] = {"error": f"{type(exc).__name__}: {exc}"}
+    sides = {}
+    del dv
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_side:
+        for name in SIDE_WORKLOADS:
+            try:
+                sides[name] = run_side(name, device, 10, peaks, not args.no_cpu_baseline)
+            except Exception as exc:   # noqa: BLE001 -- a side line never costs the headline
+                sides[name] = {"error": f"{type(exc).__name__}: {exc}"}
+    if not args.no_side and not args.no_hybrid and default_workload:
+        # the full-model workload runs on every rank (requests sharded over the GPUs)
+        try:
+            sides["hybrid"] = run_hybrid(device, 10, 3, peaks, rank, world)
+        except Exception as exc:   # noqa: BLE001
+            sides["hybrid"] = {"error": f"{type(exc).__name__}: {exc}"}
+            if world > 1:
+                raise
+    if rank == 0:
+        if sides:
             line["side"] = sides
         print(json.dumps(line), flush=True)
     if world > 1:

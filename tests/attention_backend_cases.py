@@ -6,13 +6,13 @@ from types import SimpleNamespace
 import torch
 
 
-def make_plain_case(lens, *, hq=8, hkv=2, d=128, page_size=16, seed=3, max_len=512):
+def make_plain_case(lens, *, hq=8, hkv=2, d=128, page_size=16, seed=3, max_len=512, min_slots=0):
     """``lens``: list of (cached_len, extend_len).  Returns a namespace with the pool contents (CPU),
     the page table, the requests, the new rows' q/k/v, ``out_loc`` and ``positions``."""
     g = torch.Generator().manual_seed(seed)
     n_req = len(lens)
     total = sum(c + e for c, e in lens)
-    num_slots = -(-(total + 64) // page_size) * page_size
+    num_slots = -(-max(total + 64, min_slots) // page_size) * page_size   # min_slots: one pool geometry for several cases
     perm = torch.randperm(num_slots, generator=g)
     table = torch.zeros(n_req + 2, max_len, dtype=torch.int32)
     k_pool = torch.zeros(num_slots // page_size, page_size, hkv, d, dtype=torch.bfloat16)

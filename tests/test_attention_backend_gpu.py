@@ -44,8 +44,8 @@ def test_plain_decode(cuda_device, d, hq, hkv):
 def test_decode_graph_replay_after_replanning(cuda_device):
     # the graph hooks of the plugin interface: fixed-capacity tables per batch size, a graph captured
     # on one batch keeps answering correctly after another batch is planned into the same tables
-    first = make_plain_case([(300, 1), (37, 1), (1, 1), (129, 1)], seed=5)
-    second = make_plain_case([(12, 1), (400, 1), (77, 1), (250, 1)], seed=5)
+    first = make_plain_case([(300, 1), (37, 1), (1, 1), (129, 1)], seed=5, min_slots=1024)
+    second = make_plain_case([(12, 1), (400, 1), (77, 1), (250, 1)], seed=5, min_slots=1024)
     be, pool = gpu_backend(first, cuda_device)
     be.init_capture_graph(512, [4])
     q = first.q.to(cuda_device).clone()
