@@ -162,6 +162,14 @@ class VaGdnPrefillConv(C.Structure):
     ]
 
 
+class VaAttnQkNorm(C.Structure):
+    _fields_ = [
+        ("qkv", C.c_void_p), ("qkv_row_stride", C.c_int64), ("q_weight", C.c_void_p), ("k_weight", C.c_void_p),
+        ("q_out", C.c_void_p), ("k_out", C.c_void_p), ("n", C.c_int32), ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("eps", C.c_float), ("weight_plus_one", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares is listed here
 SIGNATURES = {
     "va_abi_version": (C.c_int, []),
@@ -202,6 +210,9 @@ SIGNATURES = {
     "va_gdn_gated_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                        C.c_float, C.c_void_p]),
     "va_gdn_prefill_conv": (C.c_int, [C.POINTER(VaGdnPrefillConv), C.c_void_p]),
+    "va_attn_qk_norm": (C.c_int, [C.POINTER(VaAttnQkNorm), C.c_void_p]),
+    "va_attn_output_gate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                      C.c_void_p]),
     "va_plan_views": (C.c_int, [C.POINTER(VaPlanParams), C.POINTER(VaViewStep), C.c_void_p, C.c_int64,
                                 C.POINTER(VaPlanLayout), C.c_void_p, C.c_int64, C.POINTER(VaViewSubs)]),
 }

@@ -384,7 +384,11 @@ class SharedPrefillAttentionBuffers:
         self.cap_entries = rows
         self.cap_segments = workers * (depth + 1)
         self.cap_pages = max_pages
-        self.sizes = [self.cap_pages, self.cap_tiles * 8, self.cap_entries * 4, self.cap_segments * 8]
+        # with interleaved mRoPE the captured launch is the per-axis instantiation: the rows' (time, height,
+        # width) positions live in a fixed [3, rows] region (token index on all axes for text batches)
+        self.with_axes = a.mrope_section is not None and a.dense_engine == "tcgen05"
+        self.sizes = [self.cap_pages, self.cap_tiles * 8, self.cap_entries * 4, self.cap_segments * 8,
+                      3 * rows if self.with_axes else 0]
         self.offs = [0]
         for sz in self.sizes:
             self.offs.append(self.offs[-1] + (-(-sz // 4) * 4))
@@ -398,9 +402,12 @@ class SharedPrefillAttentionBuffers:
             self.cap_pages, self.cap_tiles, self.cap_entries, self.cap_segments)
         st.num_partials, st.num_rows, st.num_ctas = 0, rows, 0
         st.engine = DENSE_ENGINES[a.dense_engine]
+        if self.with_axes:
+            st.q_pos3 = base + 4 * self.offs[4]
+            st.mrope_lim_h, st.mrope_lim_w = a._mrope_lims
         self.event = torch.cuda.Event() if on_gpu else None
 
-    def load(self, pages, tile_arr, entries, seg_arr, n_rows) -> "DensePlan":
+    def load(self, pages, tile_arr, entries, seg_arr, n_rows, q_pos3=None) -> "DensePlan":
         if n_rows > self.rows:
             raise ValueError(f"{n_rows} query rows exceed the prepared capacity {self.rows}")
         if pages.size > self.cap_pages:
@@ -413,6 +420,12 @@ class SharedPrefillAttentionBuffers:
         hv[o[1]: o[2]] = 0             # unused tiles: zero entries
         for off, arr in zip(o, (pages, tile_arr, entries, seg_arr)):
             hv[off: off + arr.size] = arr.reshape(-1)
+        if self.with_axes:
+            axes = hv[o[4]: o[4] + 3 * self.rows].reshape(3, self.rows)   # [3, rows] with the capacity's row stride
+            axes[:] = 0
+            axes[:, :n_rows] = q_pos3 if q_pos3 is not None else entries[:n_rows, 1][None, :]
+        elif q_pos3 is not None:
+            raise NotImplementedError("these buffers were built without per-axis query positions")
         if self.blob is not self.host:
             self.blob.copy_(self.host, non_blocking=True)
             self.event.record()
@@ -861,8 +874,8 @@ class SharedCacheAttention:
             # new tokens with genuine (time, height, width) positions (attention.py:118-127)
             if self.mrope_section is None:
                 raise ValueError("PrefillSpec.mrope_rel needs an attention op built with mrope_section")
-            if self.dense_engine != "tcgen05" or graph_buffers is not None:
-                raise NotImplementedError("3-axis query positions run on the tcgen05 engine, outside graph buffers")
+            if self.dense_engine != "tcgen05":
+                raise NotImplementedError("3-axis query positions run on the tcgen05 engine")
         rel3_parts: List[np.ndarray] = []
         P = self.page_size
         widest = max(len(spec.context) + 1 for spec in specs)
@@ -980,7 +993,7 @@ class SharedCacheAttention:
         tile_arr[:, 4] = heads[order]
         pages = np.asarray(page_pool, np.int32)
         if buffers is not None:
-            return buffers.load(pages, tile_arr, entries, seg_arr, n_rows)
+            return buffers.load(pages, tile_arr, entries, seg_arr, n_rows, q_pos3=q_pos3)
         return self._pack_dense(pages, tile_arr, entries, seg_arr, n_rows, 0, q_pos3=q_pos3)
 
     def _dense_ctas(self, num_tiles: int) -> int:

@@ -6,8 +6,9 @@ with a 2x-wide q projection (query + sigmoid output gate) and per-head q/k RMSNo
 layers Hk16 / Hv32 / dk = dv = 128 with a conv window of 4; SwiGLU MLP 12288; vocabulary 151 936; bf16.
 Weights are random (there are no checkpoints here), replicated on every GPU.
 
-Projections, MLP, norms and the LM head are plain torch GEMMs / elementwise ops; the attention core
-is ``SharedCacheAttention.forward`` and the GDN layers are ``GatedDeltaNetLayer.forward_ar_decode``
+Projections, MLP, layer norms and the LM head are plain torch GEMMs / elementwise ops; the attention
+layers are ``GatedAttentionLayer`` (q/k norm, ``SharedCacheAttention.forward``, output gate) and the
+GDN layers ``GatedDeltaNetLayer.forward_ar_decode``
 -- the kernels of this package -- and the whole decode forward is captured ONCE in a CUDA graph
 through ``SharedGraphIO`` and replayed every step after the host has re-planned the step's views
 into the fixed-capacity tables.
@@ -28,6 +29,7 @@ import torch
 import torch.nn.functional as F
 
 from async_llm_b200 import AsyncContext, CacheBlock, MHAKVCache, PageAllocator, SharedCacheAttention, WorkerGroup
+from async_llm_b200.attn_layer import GatedAttentionLayer
 from async_llm_b200.gdn_layer import GatedDeltaNetLayer
 from async_llm_b200.graph_io import SharedGraphIO
 from async_llm_b200.session_plan import plan_decode_writes
@@ -112,10 +114,10 @@ class HybridDecoder:
             if cfg.is_attn(i):
                 layer.kind, layer.kv_idx = "attn", kv_idx
                 kv_idx += 1
-                layer.w_qkv = w((2 * hq + 2 * hkv) * d, h)            # [q + gate | k | v]
-                layer.q_norm = torch.zeros(d, device=self.device, dtype=torch.bfloat16)   # weight + 1 form
-                layer.k_norm = torch.zeros(d, device=self.device, dtype=torch.bfloat16)
-                layer.w_o = w(h, hq * d)
+                layer.attn = GatedAttentionLayer(
+                    layer.kv_idx, hq, hkv, d, w((2 * hq + 2 * hkv) * d, h), w(h, hq * d),   # [q | gate per head, k, v]
+                    torch.randn(d, generator=g, device=self.device) * 0.1,                 # (1 + weight) form
+                    torch.randn(d, generator=g, device=self.device) * 0.1, cfg.eps)
             else:
                 layer.kind = "gdn"
                 vdim, kdim = cfg.gdn_v_heads * dv, cfg.gdn_k_heads * dv
@@ -133,20 +135,6 @@ class HybridDecoder:
 
     def _norm(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         return F.rms_norm(x, (x.shape[-1],), weight, self.cfg.eps)
-
-    def _attention(self, layer, x: torch.Tensor, batch) -> torch.Tensor:
-        cfg = self.cfg
-        d, hq, hkv = cfg.head_dim, cfg.num_q_heads, cfg.num_kv_heads
-        n = x.shape[0]
-        q_gate, k, v = F.linear(x, layer.w_qkv).split([2 * hq * d, hkv * d, hkv * d], dim=-1)
-        q_gate = q_gate.view(n, hq, 2 * d)
-        q, gate = q_gate[..., :d], q_gate[..., d:]
-        # per-head RMSNorm with (1 + weight), minisgl/models/qwen3_5_attn.py:53-54,113-114
-        q = F.rms_norm(q, (d,), layer.q_norm + 1, cfg.eps).reshape(n, hq * d)
-        k = F.rms_norm(k.reshape(n, hkv, d), (d,), layer.k_norm + 1, cfg.eps).reshape(n, hkv * d)
-        o = batch.attn_metadata.shared_cache_op.forward(q, k, v, layer.kv_idx, batch)
-        o = (o.view(n, hq, d).float() * gate.float().sigmoid()).to(x.dtype)   # sigmoid output gate, :21-23,136
-        return F.linear(o.reshape(n, hq * d), layer.w_o)
 
     def forward(self, input_ids: torch.Tensor, batch, ar, timers: Optional[Dict[str, list]] = None) -> torch.Tensor:
         """Logits ``[rows, vocab]`` (fp32) of one decode step; ``batch`` carries the attention plan,
@@ -170,7 +158,7 @@ class HybridDecoder:
         h = self.embed[input_ids.long()]
         for layer in self.layers:
             if layer.kind == "attn":
-                h = h + timed("attn", lambda: self._attention(layer, self._norm(h, layer.norm_in), batch))
+                h = h + timed("attn", lambda: layer.attn.forward(self._norm(h, layer.norm_in), batch))
             else:
                 h = h + timed("gdn", lambda: layer.gdn.forward_ar_decode(self._norm(h, layer.norm_in), ar))
             h = h + timed("mlp", lambda: mlp(layer, h))

@@ -520,6 +520,36 @@ typedef struct VaGdnPrefillConv {
 
 int va_gdn_prefill_conv(const VaGdnPrefillConv* args, va_stream_t stream);
 
+/* 11. Gated full-attention layer steps around the view attention ---------------------------------
+ * The fused qkv projection of the reference's gated attention layer writes rows
+ *   [ head 0: q | gate ] ... [ head Hq-1: q | gate ] [ k heads ] [ v heads ]       (2*Hq + 2*Hkv) * D wide
+ * (models/qwen3_5_attn.py:47-52,103-109).
+ * va_attn_qk_norm replaces the q / gate split copies and the two per-head RMSNorm calls
+ * (models/qwen3_5_attn.py:105-114; layers/norm.py:8-22, FlashInfer's `gemma_rmsnorm` when
+ * weight_plus_one, else `rmsnorm`): q_out [n, Hq*D] and k_out [n, Hkv*D] bf16 =
+ *   x * rsqrt(mean(x^2) + eps) * (weight + (weight_plus_one ? 1 : 0)), fp32 inside, one rounding.
+ * gate and v are read where they lie by the later steps (no copy).  head_dim 128 or 256.
+ * va_attn_output_gate replaces _sigmoid_output_gate (models/qwen3_5_attn.py:21-23,136):
+ *   out = bf16(float(o) * sigmoid(float(gate))), gate read in place from the projection rows. */
+typedef struct VaAttnQkNorm {
+  const void* qkv;        /* bf16 rows, row stride in elements (multiple of 8)  */
+  int64_t qkv_row_stride;
+  const float* q_weight;  /* fp32 [head_dim]                                     */
+  const float* k_weight;  /* fp32 [head_dim]                                     */
+  void* q_out;            /* bf16 [n, num_q_heads * head_dim]                    */
+  void* k_out;            /* bf16 [n, num_kv_heads * head_dim]                   */
+  int32_t n;
+  int32_t num_q_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;
+  float eps;
+  int32_t weight_plus_one;
+} VaAttnQkNorm;
+
+int va_attn_qk_norm(const VaAttnQkNorm* args, va_stream_t stream);
+int va_attn_output_gate(const void* o, const void* qkv, int64_t qkv_row_stride, void* out, int32_t n,
+                        int32_t num_q_heads, int32_t head_dim, va_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

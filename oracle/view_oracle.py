@@ -361,3 +361,18 @@ def plain_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         out[off: off + S] = torch.einsum("shgl,lhd->shgd", torch.softmax(s_, dim=-1), V).reshape(S, num_q_heads, D)
         off += S
     return out.view(rows, -1)
+
+
+# --------------------------------------------------------------------------- gated attention layer steps
+def qk_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, weight_plus_one: bool = True) -> torch.Tensor:
+    """Per-head RMSNorm of ``x [..., D]``: ``x * rsqrt(mean(x^2) + eps) * (weight [+ 1])`` in fp32, one cast
+    back -- the published semantics of FlashInfer's ``gemma_rmsnorm`` / ``rmsnorm``, which the reference's
+    ``RMSNorm`` calls (minisgl/layers/norm.py:8-22; used at models/qwen3_5_attn.py:53-54,113-114)."""
+    xf = x.float()
+    w = weight.float() + (1.0 if weight_plus_one else 0.0)
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w).to(x.dtype)
+
+
+def sigmoid_output_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``(o.float() * gate.float().sigmoid()).to(o.dtype)`` (models/qwen3_5_attn.py:21-23)."""
+    return (o.float() * gate.float().sigmoid()).to(o.dtype)

@@ -11,7 +11,8 @@ It imports the unmodified ``minisgl.shared_cache`` from the given checkout (noth
 rebuilds the seeded cases of tests/attention_cases.py with the reference's own ``CacheBlock`` /
 ``WorkerGroup`` objects, runs ``SharedCacheAttention.prepare`` + ``forward`` (decode) and
 ``prepare_prefill_batch`` + ``forward`` (prefill) and stores the output rows as bf16 bit patterns,
-together with the rotated keys the reference stored into the pool.
+together with the rotated keys the reference stored into the pool; it also runs the reference's
+per-head q/k RMSNorm and sigmoid output gate of the gated attention layer on seeded rows (``layer/...``).
 
 ``--flashinfer-aot DIR`` points FlashInfer at prebuilt kernel modules (``DIR/<module>/<module>.so``)
 so that nothing is compiled on the GPU machine.  ``--time`` also times the reference decode forward
@@ -190,6 +191,44 @@ def time_reference_decode(handles, iters=20):
     return fwd_ms, e2e_ms
 
 
+def layer_step_inputs():
+    """Seeded inputs of the gated attention layer's steps (the tests rebuild exactly these): rows of
+    the fused qkv projection ``[n, (2*Hq + 2*Hkv) * D]``, the norm weights and an attention output."""
+    out = {}
+    for name, (n, hq, hkv, d) in {"d128": (37, 8, 2, 128), "d256": (21, 16, 4, 256)}.items():
+        g = torch.Generator().manual_seed(909 + d)
+        out[name] = dict(n=n, hq=hq, hkv=hkv, d=d, eps=1e-6,
+                         qkv=(torch.randn(n, (2 * hq + 2 * hkv) * d, generator=g) * 1.5).to(torch.bfloat16),
+                         q_weight=(torch.randn(d, generator=g) * 0.2).to(torch.bfloat16),
+                         k_weight=(torch.randn(d, generator=g) * 0.2).to(torch.bfloat16),
+                         o=torch.randn(n, hq * d, generator=g).to(torch.bfloat16))
+    return out
+
+
+def run_layer_steps(device):
+    """The reference's per-head q/k RMSNorm (``RMSNorm(..., weight_plus_one=True)``: FlashInfer
+    ``gemma_rmsnorm``, minisgl/layers/norm.py:8-22) and ``_sigmoid_output_gate``
+    (minisgl/models/qwen3_5_attn.py:21-23) on the seeded rows, as ``Qwen3_5Attention.forward`` applies
+    them (:103-114,136)."""
+    from minisgl.layers.norm import RMSNorm
+    from minisgl.models.qwen3_5_attn import _sigmoid_output_gate
+
+    res = {}
+    for name, c in layer_step_inputs().items():
+        n, hq, hkv, d = c["n"], c["hq"], c["hkv"], c["d"]
+        qkv = c["qkv"].to(device)
+        q_gate, k, _ = qkv.split([2 * hq * d, hkv * d, hkv * d], dim=-1)
+        q_gate = q_gate.view(n, hq, 2 * d)
+        q, gate = q_gate[..., :d].contiguous(), q_gate[..., d:].contiguous()
+        k = k.reshape(n, hkv, d)
+        qn, kn = RMSNorm(d, c["eps"], weight_plus_one=True), RMSNorm(d, c["eps"], weight_plus_one=True)
+        qn.weight, kn.weight = c["q_weight"].to(device), c["k_weight"].to(device)
+        res[f"layer/{name}/q"] = bf16_bits(qn.forward(q).reshape(n, hq * d))
+        res[f"layer/{name}/k"] = bf16_bits(kn.forward(k.contiguous()).reshape(n, hkv * d))
+        res[f"layer/{name}/gated"] = bf16_bits(_sigmoid_output_gate(c["o"].to(device).view(n, hq, d), gate).reshape(n, hq * d))
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("reference_python", help="directory that holds the reference's `minisgl` package")
@@ -248,6 +287,14 @@ def main():
         out[f"prefill/{name}/out"] = bf16_bits(rows_out[torch.from_numpy(rows).to(device)])
         info["cases"][f"prefill/{name}"] = {"store": store_kind, "rows": int(rows_out.shape[0])}
         print(f"prefill/{name}: {tuple(rows_out.shape)} ({store_kind})", flush=True)
+    if not only or "layer" in only:
+        try:
+            out.update(run_layer_steps(device))
+            info["layer_steps"] = "reference RMSNorm (flashinfer gemma_rmsnorm) + _sigmoid_output_gate"
+            print("layer steps: done", flush=True)
+        except Exception as exc:   # noqa: BLE001 -- the norm module may be missing; the rest still counts
+            info["layer_steps"] = f"unavailable: {type(exc).__name__}: {exc}"
+            print("layer steps unavailable:", info["layer_steps"], flush=True)
     out["info"] = np.frombuffer(json.dumps(info).encode(), dtype=np.uint8)
     os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
     np.savez_compressed(args.out, **out)

@@ -120,3 +120,52 @@ def test_prefill_with_three_axis_query_positions(cuda_device):
     assert (plain[:S0] - want[:S0]).abs().mean() > 3e-3
     assert (out[:S0].float().cpu() - plain[:S0]).abs().mean() > 3e-3
     assert torch.equal(plain[S0:], want[S0:])
+
+
+def test_three_axis_query_positions_under_fixed_prefill_buffers(cuda_device):
+    # the same batch planned into fixed-capacity prefill tables (more rows, requests and pages than it
+    # uses): the per-axis positions sit in the tables' [3, rows] region, a text-only batch planned into
+    # the same tables afterwards gets its token indices on all axes
+    from async_llm_b200 import SharedPrefillAttentionBuffers
+    from benchcases import make_prefill_case
+    rd, section, base = 64, (11, 11, 10), 1e6
+    case = make_prefill_case(lengths={"sys": 200, "doc": 333, "a": 5, "b": 0},
+                             requests=[{"context": ["sys", "doc"], "write": "a", "num_new": 70},
+                                       {"context": ["sys"], "write": "b", "num_new": 33}],
+                             num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, rope_base=base, seed=77)
+    D, Hkv, Hq, P = case.head_dim, case.num_kv_heads, case.num_q_heads, case.page_size
+    N, CAP = case.q.shape[0], 128
+    table = vo.mrope_cos_sin_cache(rd, 4096, base)
+    inv = vo.mrope_inv_freq(rd, base)
+    S0 = case.requests[0]["num_new"]
+    grid = torch.stack((torch.zeros(S0, dtype=torch.long), torch.arange(S0) // 10, torch.arange(S0) % 10))
+    pool = MHAKVCache(Hkv, 1, D, case.num_pages, P, torch.bfloat16, cuda_device)
+    attn = SharedCacheAttention(pool, torch.zeros(4096, rd), Hq, Hkv, D, P, torch.bfloat16, cuda_device,
+                                rotary_dim=rd, mrope_section=section, rope_base=base)
+    bufs = SharedPrefillAttentionBuffers(attn, workers=3, depth=3, rows=CAP, max_pages=case.num_pages)
+    assert bufs.with_axes
+    pad = lambda t, fill=0: torch.cat((t, torch.full((CAP - N, *t.shape[1:]), fill, dtype=t.dtype))).to(cuda_device)
+    q, k, v = pad(case.q), pad(case.k_new), pad(case.v_new)
+    for with_image in (True, False, True):
+        specs = case.specs()
+        if with_image:
+            specs[0].mrope_rel = grid
+        key_pos3 = torch.cat([(sp.mrope_rel if sp.mrope_rel is not None
+                               else torch.arange(sp.num_new).view(1, -1).expand(3, -1)) + sp.self_prefix_len
+                              for sp in specs], dim=1)
+        pool.k_cache(0).copy_(case.k_pool)
+        pool.v_cache(0).copy_(case.v_pool)
+        meta = attn.prepare_prefill_batch(specs, graph_buffers=bufs)
+        pos3 = torch.zeros(3, CAP, dtype=torch.long)
+        pos3[:, :N] = key_pos3
+        batch = SimpleNamespace(attn_metadata=meta, positions=pad(case.positions), out_loc=pad(case.out_loc, -1),
+                                mrope_positions=pos3.to(cuda_device))
+        out = attn.forward(q, k, v, 0, batch)
+        torch.cuda.synchronize()
+        attn.check_status()
+        k_ref, v_ref = case.k_pool.clone(), case.v_pool.clone()
+        k_ref.view(-1, Hkv, D)[case.out_loc.long()] = vo.rope_mrope(case.k_new.view(N, Hkv, D), key_pos3, inv, section, rd)
+        v_ref.view(-1, Hkv, D)[case.out_loc.long()] = case.v_new.view(N, Hkv, D)
+        assert torch.equal(pool.k_cache(0).cpu(), k_ref)
+        want = vo.view_prefill(case.q, k_ref, v_ref, specs, table, Hq, rotary_dim=rd, mrope=(inv, section))
+        assert_close_bf16(out[:N], want, f"fixed prefill buffers, image rows: {with_image}")
