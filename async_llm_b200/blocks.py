@@ -28,41 +28,125 @@ class _TrackedDict(dict):
     Mirrors the invalidation contract of the reference ``StateDict``
     (minisgl/shared_cache/gdn_state.py:15-58): planners may cache per-block
     address tables and must notice when a state tensor is replaced.
+
+    A publisher that replaces every entry at once (one decode step writes all layers of a block) may
+    hand the entries over as a producer (``defer``): the per-layer tensor views are then only built
+    when somebody reads the dictionary -- the kernels work from the cached addresses and never do.
     """
 
     def __init__(self, owner: "CacheBlock", values=()):
         super().__init__(values)
         self._owner = owner
+        self._deferred = None      # zero-argument callable returning the (key, value) pairs still to be merged
+        self._deferred_keys = frozenset()
 
     def _touch(self) -> None:
         self._owner._gdn_revision += 1
 
+    def _sync(self) -> None:
+        producer = self._deferred
+        if producer is not None:
+            self._deferred, self._deferred_keys = None, frozenset()
+            super().update(producer())
+
+    def defer(self, producer, keys) -> None:
+        """Replace-or-add the entries ``producer()`` yields (their keys are ``keys``), lazily.  Counts
+        as a mutation now.  An earlier deferred update that this one overwrites completely is dropped
+        unbuilt; otherwise it goes in first, so that later entries win."""
+        self._touch()
+        keys = frozenset(keys)
+        if self._deferred is not None and not self._deferred_keys <= keys:
+            self._sync()
+        self._deferred, self._deferred_keys = producer, keys
+
+    def known_keys(self) -> set:
+        """The dictionary's keys, pending ones included, without building anything."""
+        return set(dict.keys(self)) | self._deferred_keys
+
+    # -- reads: merge what is pending first
+    def __getitem__(self, key):
+        self._sync()
+        return super().__getitem__(key)
+
+    def get(self, key, default=None):
+        self._sync()
+        return super().get(key, default)
+
+    def __contains__(self, key):
+        self._sync()
+        return super().__contains__(key)
+
+    def __iter__(self):
+        self._sync()
+        return super().__iter__()
+
+    def __len__(self):
+        self._sync()
+        return super().__len__()
+
+    def keys(self):
+        self._sync()
+        return super().keys()
+
+    def values(self):
+        self._sync()
+        return super().values()
+
+    def items(self):
+        self._sync()
+        return super().items()
+
+    def copy(self):
+        self._sync()
+        return dict(super().items())
+
+    def __eq__(self, other):
+        self._sync()
+        return super().__eq__(other)
+
+    def __ne__(self, other):
+        return not self.__eq__(other)
+
+    __hash__ = None
+
+    def __repr__(self):
+        self._sync()
+        return super().__repr__()
+
+    # -- mutations
     def __setitem__(self, key, value):
         self._touch()
+        self._sync()
         super().__setitem__(key, value)
 
     def __delitem__(self, key):
         self._touch()
+        self._sync()
         super().__delitem__(key)
 
     def clear(self):
         self._touch()
+        self._deferred, self._deferred_keys = None, frozenset()
         super().clear()
 
     def pop(self, key, *default):
         self._touch()
+        self._sync()
         return super().pop(key, *default)
 
     def popitem(self):
         self._touch()
+        self._sync()
         return super().popitem()
 
     def update(self, *args, **kwargs):
         self._touch()
+        self._sync()
         super().update(*args, **kwargs)
 
     def setdefault(self, key, default=None):
-        if key not in self:
+        self._sync()
+        if not super().__contains__(key):
             self._touch()
         return super().setdefault(key, default)
 

@@ -30,7 +30,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .blocks import CacheBlock
+from .blocks import CacheBlock, _TrackedDict
 
 GDN_ENGINES = {"scan": 0, "chunk": 1}   # VA_GDN_ENGINE_* of the C header
 
@@ -356,25 +356,45 @@ class SharedCacheGDN:
             layers = st["layers"]
             # the new summaries' addresses are known without touching the tensors again: [W, L, 2]
             new_ptrs = np.ascontiguousarray(st["host"][ROW_WRITE_A:ROW_WRITE_B + 1, :, :, 0].transpose(2, 1, 0))
+            conv_layers = sorted(st["conv_layers"])
             for w, target in enumerate(st["targets"]):
-                if st["out_b"] is None:
-                    slab_a = slab_b = st["out_a"][w]
-                    rows = slab_a.unbind(0)
-                    pairs = zip(rows[:layers], rows[layers:])
+                slab_a = st["out_a"][w]
+                slab_b = slab_a if st["out_b"] is None else st["out_b"][w]
+                conv_slab = st["conv_out"][w]
+
+                def affine_items(slab_a=slab_a, slab_b=slab_b):
+                    if slab_b is slab_a:
+                        rows = slab_a.unbind(0)
+                        return zip(range(layers), zip(rows[:layers], rows[layers:]))
+                    return zip(range(layers), zip(slab_a.unbind(0), slab_b.unbind(0)))
+
+                def conv_items(conv_slab=conv_slab):
+                    rows = conv_slab.unbind(0)
+                    return [(layer, rows[layer]) for layer in conv_layers]
+
+                affine, conv = target.linear_affine, target.linear_conv_state
+                lazy = isinstance(affine, _TrackedDict) and isinstance(conv, _TrackedDict)
+                if lazy:
+                    # the per-layer views (48 + 24 tensor objects per worker) are only built if somebody
+                    # reads the dictionaries; the kernels work from the addresses cached below
+                    affine.defer(affine_items, range(layers))
+                    if conv_layers:
+                        conv.defer(conv_items, conv_layers)
+                    full_a = affine.known_keys() == set(range(layers))
+                    full_c = conv.known_keys() == set(range(layers))
                 else:
-                    slab_a, slab_b = st["out_a"][w], st["out_b"][w]
-                    pairs = zip(slab_a.unbind(0), slab_b.unbind(0))
-                target.linear_affine.update(zip(range(layers), pairs))
-                if st["conv_layers"]:
-                    conv_rows = st["conv_out"][w].unbind(0)
-                    target.linear_conv_state.update({layer: conv_rows[layer] for layer in st["conv_layers"]})
+                    affine.update(affine_items())
+                    if conv_layers:
+                        conv.update(conv_items())
+                    full_a = len(affine) == layers
+                    full_c = len(conv) == layers
                 if not hasattr(target, "_gdn_revision"):
                     continue
-                if len(target.linear_affine) == layers:
+                if full_a:
                     target._gdn_ptr_cache = (target._gdn_revision, self.device, new_ptrs[w], [slab_a, slab_b])
-                if len(st["conv_layers"]) == layers and len(target.linear_conv_state) == layers:
+                if len(conv_layers) == layers and full_c:
                     target._gdn_conv_cache = (target._gdn_revision, self.device,
-                                              np.ascontiguousarray(st["host"][ROW_CONV_WRITE, :, w, 0]), [st["conv_out"][w]])
+                                              np.ascontiguousarray(st["host"][ROW_CONV_WRITE, :, w, 0]), [conv_slab])
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream(self.device))

@@ -449,7 +449,8 @@ def side_gdn_prefill(device, iters, peaks, with_cpu):
     return res
 
 
-def run_hybrid(device, steps: int, warmup: int, peaks, rank: int, world: int, per_gpu: int = 32) -> dict:
+def run_hybrid(device, steps: int, warmup: int, peaks, rank: int, world: int, per_gpu: int = 32,
+               profile_one_step: bool = False) -> dict:
     """Config 5: the random-init hybrid decoder ([GDN, GDN, GDN, attention] x 8) decoding over cache
     views, requests sharded over the GPUs.  Every rank takes part; returns the line on every rank
     (rank 0 prints it).  A step = partition of the global request list, write planning, attention +
@@ -536,6 +537,13 @@ def run_hybrid(device, steps: int, warmup: int, peaks, rank: int, world: int, pe
     for k in range(warmup):
         step(k)
     barrier()
+    if profile_one_step:
+        # one step between cudaProfilerStart / Stop, for `ncu --profile-from-start off`
+        torch.cuda.profiler.start()
+        step(warmup)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return {"kernel_only": True, "workload": "hybrid"}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(device.index or 0) as clocks:
         e0.record()
@@ -650,7 +658,8 @@ def main() -> None:
                         args.page_size) == (REQUESTS, SHARED_LEN, PRIVATE_LEN, 16, 2, 256, PAGE_SIZE)
 
     if args.workload == "hybrid":
-        line = run_hybrid(device, max(3, args.steps), args.warmup, peaks, rank, world)
+        line = run_hybrid(device, max(3, args.steps), args.warmup, peaks, rank, world,
+                          profile_one_step=args.kernel_only)
         if rank == 0:
             print(json.dumps(line), flush=True)
         if world > 1:

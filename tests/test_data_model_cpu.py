@@ -123,3 +123,35 @@ def test_write_planning_borrows_one_page_per_full_block():
     assert starts.tolist() == [8, 12] and token_slots.tolist() == [22, 23, 8, 9, 10, 11, 12]
     starts, token_slots = alloc_token_storage(alloc, P, CPU, 3)
     assert starts.tolist() == [16] and token_slots.tolist() == [16, 17, 18]
+
+
+def test_state_dictionaries_build_deferred_entries_only_when_read():
+    # a publisher may hand a block's per-layer entries over as a producer; nothing is built until the
+    # dictionary is read, a later complete hand-over drops an earlier unbuilt one, and every hand-over
+    # counts as a mutation for the planners' caches
+    b = CacheBlock(torch.device("cpu"), 16)
+    built = []
+
+    def producer(tag):
+        def make():
+            built.append(tag)
+            return [(layer, (tag, layer)) for layer in range(3)]
+        return make
+
+    rev = b._gdn_revision
+    b.linear_affine.defer(producer("first"), range(3))
+    assert b._gdn_revision > rev and built == []
+    assert b.linear_affine.known_keys() == {0, 1, 2}
+    b.linear_affine.defer(producer("second"), range(3))
+    assert built == []                                   # the first hand-over was overwritten unbuilt
+    assert b.linear_affine[1] == ("second", 1) and built == ["second"]
+    assert len(b.linear_affine) == 3 and 2 in b.linear_affine and list(b.linear_affine) == [0, 1, 2]
+    b.linear_affine.defer(producer("third"), range(3))
+    b.linear_affine[7] = "x"                             # a plain write merges what is pending first
+    assert built == ["second", "third"] and b.linear_affine.get(0) == ("third", 0) and b.linear_affine[7] == "x"
+    b.linear_affine.defer(producer("fourth"), range(3))
+    b.linear_affine.defer(lambda: [(9, "nine")], [9])    # a partial hand-over keeps the earlier one
+    assert dict(b.linear_affine.items()) == {0: ("fourth", 0), 1: ("fourth", 1), 2: ("fourth", 2), 7: "x", 9: "nine"}
+    b.linear_affine.defer(producer("fifth"), range(3))
+    b.clear()
+    assert len(b.linear_affine) == 0 and "fifth" not in built
