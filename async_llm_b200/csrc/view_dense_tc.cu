@@ -26,14 +26,18 @@
 //   MMA        walks the schedule converged (waits included); the elected lane issues the products
 //              and the commits that signal mbarriers.
 //   loaders    rotate-and-stage the tile's queries per segment (RoPE delta entry.rel +
-//              segment.loc_base); gather K/V rows through the page table with 16-byte cp.async
-//              into 128-byte-swizzled tiles, copying along rows (coalesced in global memory,
-//              conflict-free in shared memory); the same tile layout is the K-major B operand of
-//              S and the MN-major B operand of PV.
+//              segment.loc_base); fetch K/V tiles through the page table into 128-byte-swizzled
+//              tiles: whole pages as TMA boxes (cp.async.bulk.tensor, one box per page and
+//              128-byte panel, completion counted on the slot's mbarrier), ragged pages and
+//              zero rows with 16-byte cp.async along rows; the same tile layout is the K-major
+//              B operand of S and the MN-major B operand of PV.
 //              A ring slot has exactly one producer warp: an mbarrier parity wait may only target
 //              the current or the preceding phase.
 // Every mbarrier wait is bounded; on expiry the CTA records VA_DEV_WAIT_EXPIRED, all
 // roles leave their loops, TMEM is freed and the kernel returns.
+#include <cuda.h>
+
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -75,6 +79,12 @@ struct TcParams {
   int32_t* status;
   const int32_t* q_pos3;   // [3, num_rows] per-axis rotation positions of the query rows, or null
   int32_t mrope_lim_h, mrope_lim_w;
+  // Tensor maps of the K and V pools seen as [num_slots, num_kv_heads * head_dim] bf16 matrices, box
+  // = one page of rows x 64 elements, SWIZZLE_128B: one box is one page of one 128-byte panel of a
+  // tile.  use_tma = 0: no maps (page size or alignment does not fit), every row is gathered.
+  int32_t use_tma;
+  alignas(64) CUtensorMap tmap_k;
+  alignas(64) CUtensorMap tmap_v;
 };
 
 constexpr int kRows = 128;           // query rows per stream (TMEM lanes)
@@ -280,6 +290,20 @@ __device__ __forceinline__ void tmem_st16_issue(uint32_t taddr, const uint32_t (
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
+// One box of a tiled tensor map, global -> shared, completion counted in bytes on an mbarrier.
+// x (elements of the innermost dimension) times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+
 // barrier slots (8 bytes each) in the barrier area
 enum Bar : int {
   kBarQFull = 0, kBarQEmpty = 1, kBarFull = 2, kBarEmpty = 7, kBarSFull = 12, kBarPFull = 14,
@@ -288,7 +312,9 @@ enum Bar : int {
 
 // kAxes: the queries carry per-axis (interleaved mRoPE) positions, p.q_pos3; a separate
 // instantiation, so that the common path pays nothing for it.
-template <int D, bool kAxes>
+// kTma: whole pages of K/V arrive as TMA boxes (the host has encoded tensor maps of the pools);
+// otherwise every row is gathered with cp.async (pages of fewer than 8 rows).
+template <int D, bool kAxes, bool kTma>
 __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(const __grid_constant__ TcParams p) {
   using Cfg = TcCfg<D>;
   constexpr int BN = Cfg::kBN;
@@ -347,6 +373,7 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
   uint32_t ru[2] = {0u, 0u};
   bool dead = false;
   bool q_release_pending = false;  // MMA warp: the staged queries' QEmpty commit is still owed
+  uint32_t last_fill = 0xffffffffu;  // loader warp: ring unit it filled last (none yet)
   // Bounded wait.  A role that gives up raises the CTA-wide abort flag, which every other wait
   // polls, so one expiry takes all roles out of their loops.
   auto wait = [&](int slot, uint32_t parity) -> bool {
@@ -529,10 +556,15 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
           ++q_idx;
         }
         }
-        // ---- K and V tiles of this segment: this warp fills the ring units that map to its slot
+        // ---- K and V tiles of this segment: this warp fills the ring units that map to its slot.
+        // Pages that lie wholly inside the segment arrive as TMA boxes (one per page and 128-byte
+        // panel, issued by the lane that looked the page up); the ragged last page, the rows past the
+        // segment's end (zero-filled) and segments that do not start on a page boundary are
+        // gathered row by row with cp.async.
         const int page_off = seg_field(s, 0);
         const int tok_begin = seg_field(s, 1);
         const int n_tiles = (n_keys + BN - 1) / BN;
+        const bool seg_tma = kTma && tok_begin % P == 0;
         for (int t = 0; t < n_tiles && !dead; ++t, ++j) {
 #pragma unroll 1
           for (int is_v = 0; is_v < 2 && !dead; ++is_v) {
@@ -540,24 +572,37 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
             if (static_cast<int>(u % NSLOT) != lw) continue;
             const uint32_t dst = smem_base + Cfg::kOffRing + lw * Cfg::kTileBytes;
             const __nv_bfloat16* pool = is_v ? p.v_pool : p.k_pool;
-            // physical slot of keys lane, lane+32, ... of this tile (-1 past the segment's end):
+            const int tma_pages = seg_tma ? min(BN, n_keys - t * BN) / P : 0;   // at most BN / 8 <= 16
+            const int tma_rows = tma_pages * P;
+            int my_page = -1;   // page of box `lane`
+            if (lane < tma_pages) {
+              const int pidx = page_off + (tok_begin + t * BN) / P + lane;
+              if (pidx >= 0 && pidx < p.num_page_indices) {
+                const int page = __ldg(p.page_indices + pidx);
+                if (page >= 0 && page < p.num_pages) my_page = page;
+              }
+              if (my_page < 0) report(p.status, VA_DEV_BAD_PAGE);
+            }
+            // gathered tile: physical slot of keys lane, lane+32, ... (-1 past the segment's end),
             // one page-table read per key, shared with the other lanes by shuffle
             int my_slot[BN / 32];
+            if constexpr (!kTma) {
 #pragma unroll
-            for (int i = 0; i < BN / 32; ++i) {
-              const int kk = t * BN + i * 32 + lane;
-              int slot = -1;
-              if (kk < n_keys) {
-                const int tok = tok_begin + kk;
-                const int pg = tok / P;
-                const int pidx = page_off + pg;
-                if (pidx >= 0 && pidx < p.num_page_indices) {
-                  const int page = __ldg(p.page_indices + pidx);
-                  if (page >= 0 && page < p.num_pages) slot = page * P + (tok - pg * P);
+              for (int i = 0; i < BN / 32; ++i) {
+                const int kk = t * BN + i * 32 + lane;
+                int slot = -1;
+                if (kk < n_keys) {
+                  const int tok = tok_begin + kk;
+                  const int pg = tok / P;
+                  const int pidx = page_off + pg;
+                  if (pidx >= 0 && pidx < p.num_page_indices) {
+                    const int page = __ldg(p.page_indices + pidx);
+                    if (page >= 0 && page < p.num_pages) slot = page * P + (tok - pg * P);
+                  }
+                  if (slot < 0) report(p.status, VA_DEV_BAD_PAGE);
                 }
-                if (slot < 0) report(p.status, VA_DEV_BAD_PAGE);
+                my_slot[i] = slot;
               }
-              my_slot[i] = slot;
             }
             // the page-table reads above are in flight while the slot is still being consumed
             if (!wait(kBarEmpty + lw, ((u / NSLOT) & 1u) ^ 1u)) break;
@@ -567,19 +612,55 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
             constexpr int kLanesPerRow = 32 / kRowsPerCopy;
             const int chunk = lane % kLanesPerRow;
             const int sub = lane / kLanesPerRow;
+            if constexpr (!kTma) {
 #pragma unroll
-            for (int it = 0; it < BN / kRowsPerCopy; ++it) {
-              const int key = it * kRowsPerCopy + sub;
-              const int slot = __shfl_sync(0xffffffffu, my_slot[(it * kRowsPerCopy) >> 5], key & 31);
-              const int64_t row_off = static_cast<int64_t>(slot < 0 ? 0 : slot) * slot_stride +
-                                      static_cast<int64_t>(kvh) * D;
-              cp_async16_hint(dst + sw_off(key, chunk, BN), pool + row_off + chunk * 8, slot < 0 ? 0 : 16, kv_policy);
+              for (int it = 0; it < BN / kRowsPerCopy; ++it) {
+                const int key = it * kRowsPerCopy + sub;
+                const int slot = __shfl_sync(0xffffffffu, my_slot[(it * kRowsPerCopy) >> 5], key & 31);
+                const int64_t row_off = static_cast<int64_t>(slot < 0 ? 0 : slot) * slot_stride +
+                                        static_cast<int64_t>(kvh) * D;
+                cp_async16_hint(dst + sw_off(key, chunk, BN), pool + row_off + chunk * 8, slot < 0 ? 0 : 16, kv_policy);
+              }
+            } else {
+              const bool mine = lane < tma_pages && my_page >= 0;
+              const uint32_t boxes = __popc(__ballot_sync(0xffffffffu, mine));
+              if (lane == 0) mbar_expect_tx(bar(kBarFull + lw), boxes * static_cast<uint32_t>(P * D * 2));
+              __syncwarp();
+              if (mine) {
+                const CUtensorMap* map = is_v ? &p.tmap_v : &p.tmap_k;
+#pragma unroll
+                for (int pn = 0; pn < D / 64; ++pn)
+                  tma_load_2d(dst + pn * (BN * 128) + lane * (P * 128), map, kvh * D + pn * 64, my_page * P,
+                              bar(kBarFull + lw), kv_policy);
+              }
+              // rows after the boxes: the segment's ragged last page, then zero rows
+#pragma unroll 1
+              for (int key = tma_rows + sub; key < BN; key += kRowsPerCopy) {
+                const int kk = t * BN + key;
+                int slot = -1;
+                if (kk < n_keys) {
+                  const int tok = tok_begin + kk;
+                  const int pg = tok / P;
+                  const int pidx = page_off + pg;
+                  if (pidx >= 0 && pidx < p.num_page_indices) {
+                    const int page = __ldg(p.page_indices + pidx);
+                    if (page >= 0 && page < p.num_pages) slot = page * P + (tok - pg * P);
+                  }
+                  if (slot < 0) report(p.status, VA_DEV_BAD_PAGE);
+                }
+                const int64_t row_off = static_cast<int64_t>(slot < 0 ? 0 : slot) * slot_stride +
+                                        static_cast<int64_t>(kvh) * D;
+                cp_async16_hint(dst + sw_off(key, chunk, BN), pool + row_off + chunk * 8, slot < 0 ? 0 : 16, kv_policy);
+              }
             }
-            cp_async_commit();
-            cp_async_wait<0>();  // this lane's part of the tile has landed
-            fence_proxy_async();
+            if (tma_rows < BN) {
+              cp_async_commit();
+              cp_async_wait<0>();  // this lane's part of the tile has landed
+              fence_proxy_async();
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kBarFull + lw));
+            last_fill = u;
           }
         }
       }
@@ -916,6 +997,10 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
       run_tiles(std::integral_constant<int, 1>{});
     } else if (warp < Cfg::kLoaderWarp0 + Cfg::kLoaderWarps) {
       run_tiles(std::integral_constant<int, 0>{});
+      // no box may still be on its way into shared memory when the CTA exits (only possible after
+      // an abort: otherwise the MMA warp has consumed every filled slot)
+      if (last_fill != 0xffffffffu)
+        mbar_wait_bounded(bar(kBarFull + (warp - Cfg::kLoaderWarp0)), (last_fill / NSLOT) & 1u, kTcPolls);
     }  // padding warps of the last warpgroup have no work
   }
 
@@ -929,13 +1014,51 @@ __global__ void __launch_bounds__(TcCfg<D>::kThreads, 1) view_dense_tc_kernel(co
 template <int D>
 int launch_tc(const TcParams& p, int num_ctas, cudaStream_t stream) {
   using Cfg = TcCfg<D>;
-  auto kernel = p.q_pos3 != nullptr ? view_dense_tc_kernel<D, true> : view_dense_tc_kernel<D, false>;
+  auto kernel = p.use_tma != 0
+                    ? (p.q_pos3 != nullptr ? view_dense_tc_kernel<D, true, true> : view_dense_tc_kernel<D, false, true>)
+                    : (p.q_pos3 != nullptr ? view_dense_tc_kernel<D, true, false> : view_dense_tc_kernel<D, false, false>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kTotalBytes);
   if (e != cudaSuccess) return va_host::note_cuda_error(e);
   kernel<<<num_ctas, Cfg::kThreads, Cfg::kTotalBytes, stream>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return va_host::note_cuda_error(e);
   return VA_OK;
+}
+
+// cuTensorMapEncodeTiled, looked up through the runtime (no link against the driver library)
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static const EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+// VA_DENSE_TMA=0 in the environment keeps every K/V row on the cp.async gather (for comparisons)
+bool tma_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("VA_DENSE_TMA");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on && encode_tiled_fn() != nullptr;
+}
+// pool [num_slots, row_elems] bf16, box = page_size rows x 64 elements, 128-byte swizzle
+bool encode_pool_map(CUtensorMap* map, const void* base, int64_t row_elems, int64_t num_slots, int page_size) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_elems), static_cast<cuuint64_t>(num_slots)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_elems) * 2};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(page_size)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                                       strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -975,6 +1098,19 @@ int va_dense_tc_launch(const VaPool* pool, const VaDensePlan* plan, const void* 
   p.q_pos3 = plan->q_pos3;
   p.mrope_lim_h = plan->mrope_lim_h;
   p.mrope_lim_w = plan->mrope_lim_w;
+  p.use_tma = 0;
+  {
+    // TMA boxes need pages of a multiple of 8 rows (a box must start on a swizzle atom of the
+    // tile) that divide the key tile, and 16-byte aligned pools and row strides.
+    const int bn = pool->head_dim == 128 ? TcCfg<128>::kBN : TcCfg<256>::kBN;
+    const int64_t row_elems = static_cast<int64_t>(pool->num_kv_heads) * pool->head_dim;
+    const bool fits = tma_enabled() && (pool->head_dim == 128 || pool->head_dim == 256) && pool->page_size >= 8 &&
+                      pool->page_size % 8 == 0 && bn % pool->page_size == 0 && pool->num_slots > 0 &&
+                      (reinterpret_cast<uintptr_t>(pool->k) & 15u) == 0 && (reinterpret_cast<uintptr_t>(pool->v) & 15u) == 0;
+    if (fits && encode_pool_map(&p.tmap_k, pool->k, row_elems, pool->num_slots, pool->page_size) &&
+        encode_pool_map(&p.tmap_v, pool->v, row_elems, pool->num_slots, pool->page_size))
+      p.use_tma = 1;
+  }
   int sms = va_sm_count();
   if (sms <= 0) return VA_ERR_LAUNCH;
   int ctas = plan->num_ctas > 0 ? plan->num_ctas : sms;

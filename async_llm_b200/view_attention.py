@@ -721,7 +721,8 @@ class SharedCacheAttention:
     DENSE_TILES_PER_CTA = 1  # key chunks are sized so that every dense CTA runs this many tiles
     STREAM_RATE = {256: 31.0, 128: 60.0}
     DENSE_RATE = {256: 10.0, 128: 25.0}          # mma.sync tiles
-    DENSE_RATE_TCGEN05 = {256: 16.0, 128: 30.0}  # tcgen05 tiles
+    DENSE_RATE_TCGEN05 = {256: 16.0, 128: 30.0}  # tcgen05 tiles, K/V rows gathered (pages of fewer than 8 tokens)
+    DENSE_RATE_TCGEN05_TMA = {256: 20.0, 128: 30.0}  # tcgen05 tiles, whole pages fetched as TMA boxes
 
     def _run_planner(self, call, n_sub_bound: int, n_pages: int, W: int, buffers=None) -> DecodePlan:
         """Run a native planner entry point (``call(params, blob_ptr, blob_words, layout)``) into
@@ -734,7 +735,12 @@ class SharedCacheAttention:
         else:
             G_max = getattr(self, "_lanes", None) or 592
             width = getattr(self, "_lane_width", 1)
-        rates = self.DENSE_RATE_TCGEN05 if self.dense_engine == "tcgen05" else self.DENSE_RATE
+        if self.dense_engine != "tcgen05":
+            rates = self.DENSE_RATE
+        elif self.page_size % 8 == 0 and self.page_size <= 64:
+            rates = self.DENSE_RATE_TCGEN05_TMA
+        else:
+            rates = self.DENSE_RATE_TCGEN05
         pp = self._plan_params
         pp.num_workers, pp.num_kv_heads = W, H
         pp.readers_per_tile = self.tile_rows() // self.gqa
