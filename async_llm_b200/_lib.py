@@ -87,6 +87,8 @@ class VaGdnStep(C.Structure):
         ("num_workers", C.c_int32), ("depth", C.c_int32), ("num_k_heads", C.c_int32),
         ("num_v_heads", C.c_int32), ("head_k_dim", C.c_int32), ("head_v_dim", C.c_int32),
         ("l2_eps", C.c_float), ("q_scale", C.c_float), ("status", C.c_void_p),
+        ("q_row_stride", C.c_int64), ("k_row_stride", C.c_int64), ("v_row_stride", C.c_int64),
+        ("summary_dtype", C.c_int32),
     ]
 
 
@@ -99,7 +101,7 @@ class VaGdnPrefill(C.Structure):
         ("num_requests", C.c_int32), ("num_k_heads", C.c_int32), ("num_v_heads", C.c_int32),
         ("head_k_dim", C.c_int32), ("head_v_dim", C.c_int32), ("l2_eps", C.c_float), ("q_scale", C.c_float),
         ("engine", C.c_int32), ("max_segment_tokens", C.c_int32), ("scratch", C.c_void_p),
-        ("scratch_bytes", C.c_int64), ("num_tokens", C.c_int64),
+        ("scratch_bytes", C.c_int64), ("num_tokens", C.c_int64), ("summary_dtype", C.c_int32),
     ]
 
 
@@ -149,7 +151,7 @@ class VaGdnDecodePre(C.Structure):
         ("g_out", C.c_void_p), ("beta_f32_out", C.c_void_p), ("prior_conv_ptrs", C.c_void_p),
         ("conv_out_ptrs", C.c_void_p), ("num_workers", C.c_int32), ("conv_dim", C.c_int32),
         ("conv_kernel", C.c_int32),
-        ("num_v_heads", C.c_int32),
+        ("num_v_heads", C.c_int32), ("a_row_stride", C.c_int64), ("b_row_stride", C.c_int64),
     ]
 
 
@@ -168,6 +170,19 @@ class VaAttnQkNorm(C.Structure):
         ("q_out", C.c_void_p), ("k_out", C.c_void_p), ("n", C.c_int32), ("num_q_heads", C.c_int32),
         ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("eps", C.c_float), ("weight_plus_one", C.c_int32),
     ]
+
+
+SUMMARY_F32, SUMMARY_BF16 = 0, 1   # VA_SUMMARY_*
+
+
+def summary_code(dtype) -> int:
+    """VA_SUMMARY_* of a torch dtype of block summaries."""
+    import torch
+    if dtype == torch.float32:
+        return SUMMARY_F32
+    if dtype == torch.bfloat16:
+        return SUMMARY_BF16
+    raise ValueError("Shared GDN state dtype must be float32 or bfloat16")
 
 
 # name -> (restype, argtypes); every symbol the header declares is listed here
@@ -191,7 +206,7 @@ SIGNATURES = {
                                         C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "va_gdn_step": (C.c_int, [C.POINTER(VaGdnStep), C.c_void_p]),
     "va_gdn_compose": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
-                                 C.c_int32, C.c_int32, C.c_void_p]),
+                                 C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "va_gdn_prefill_scratch_bytes": (C.c_int64, [C.c_int64, C.c_int32]),
     "va_gdn_prefill": (C.c_int, [C.POINTER(VaGdnPrefill), C.c_void_p]),
     "va_plan_decode": (C.c_int, [C.POINTER(VaPlanParams), C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -200,7 +215,7 @@ SIGNATURES = {
     "va_block_copy": (C.c_int, [C.POINTER(VaPool), C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_int32,
                                 C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "va_gdn_compose_pairs": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                       C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+                                       C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "va_mrope_rotate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "va_store_kv_mrope": (C.c_int, [C.POINTER(VaPool), C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
@@ -208,7 +223,7 @@ SIGNATURES = {
                                     C.c_void_p]),
     "va_gdn_decode_pre": (C.c_int, [C.POINTER(VaGdnDecodePre), C.c_void_p]),
     "va_gdn_gated_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
-                                       C.c_float, C.c_void_p]),
+                                       C.c_float, C.c_int32, C.c_int64, C.c_void_p]),
     "va_gdn_prefill_conv": (C.c_int, [C.POINTER(VaGdnPrefillConv), C.c_void_p]),
     "va_attn_qk_norm": (C.c_int, [C.POINTER(VaAttnQkNorm), C.c_void_p]),
     "va_attn_output_gate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,

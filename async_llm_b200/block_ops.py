@@ -33,8 +33,10 @@ class BlockOps:
 
     def __init__(self, kv_cache, page_allocator, sc_attn, page_size: int, device,
                  state_dtype: torch.dtype = torch.float32) -> None:
-        if state_dtype != torch.float32:
-            raise NotImplementedError("GDN block summaries are composed in float32 only")
+        # storage type of the GDN summaries; composed in fp32, bf16 results rounded once after the
+        # fp32 add (minisgl/shared_cache/gdn_affine.py:113-122)
+        self._summary_code = _lib.summary_code(state_dtype)
+        self.state_dtype = state_dtype
         self.kv_cache = kv_cache
         self.page_allocator = page_allocator
         self.sc_attn = sc_attn
@@ -151,7 +153,7 @@ class BlockOps:
         rows = [[], [], [], [], [], []]
         heads, dv, dk = pairs[0][1].shape[-3:]
         for a1, b1, a2, b2 in pairs:
-            tensors = [t.to(device=self.device, dtype=torch.float32).contiguous() for t in (a1, b1, a2, b2)]
+            tensors = [t.to(device=self.device, dtype=self.state_dtype).contiguous() for t in (a1, b1, a2, b2)]
             if not tensors[0].is_cuda:
                 raise RuntimeError("block merge runs the CUDA compose kernel: there is no CPU fallback")
             out_a, out_b = torch.empty_like(tensors[0]), torch.empty_like(tensors[1])
@@ -161,7 +163,7 @@ class BlockOps:
                 row.append(t.data_ptr())
         table = torch.tensor(rows, dtype=torch.int64).to(self.device)
         rc = _lib.lib().va_gdn_compose_pairs(*(table[i].data_ptr() for i in range(6)), len(pairs), heads, dk, dv,
-                                             _lib.stream_ptr())
+                                             self._summary_code, _lib.stream_ptr())
         _lib.check(rc, "va_gdn_compose_pairs")
         return outs
 

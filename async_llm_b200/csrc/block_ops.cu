@@ -148,6 +148,7 @@ struct PairParams {
   const int64_t* out_b;
   int32_t num_pairs;
   int32_t heads;
+  int32_t summary_bf16;   // the tensors are bf16 (fp32 otherwise); sums in fp32, one rounding per output
 };
 
 constexpr int kDim = 128;   // head_k_dim = head_v_dim
@@ -165,10 +166,11 @@ __global__ void __launch_bounds__(256) gdn_compose_pairs_kernel(const __grid_con
   const int which = blockIdx.z & 1;
   const int row0 = (tile >> 1) * kTile, col0 = (tile & 1) * kTile;
   const int64_t head_off = static_cast<int64_t>(head) * kDim * kDim;
-  const float* x = reinterpret_cast<const float*>(which ? p.b_first[pair] : p.a_first[pair]) + head_off;
-  const float* y = reinterpret_cast<const float*>(p.a_second[pair]) + head_off;
-  const float* add = which ? reinterpret_cast<const float*>(p.b_second[pair]) + head_off : nullptr;
-  float* out = reinterpret_cast<float*>(which ? p.out_b[pair] : p.out_a[pair]) + head_off;
+  const bool bf16 = p.summary_bf16 != 0;
+  const void* x = reinterpret_cast<const void*>(which ? p.b_first[pair] : p.a_first[pair]);
+  const void* y = reinterpret_cast<const void*>(p.a_second[pair]);
+  const void* add = which ? reinterpret_cast<const void*>(p.b_second[pair]) : nullptr;
+  void* out = reinterpret_cast<void*>(which ? p.out_b[pair] : p.out_a[pair]);
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4] = {};
   for (int k0 = 0; k0 < kDim; k0 += kChunk) {
@@ -177,9 +179,9 @@ __global__ void __launch_bounds__(256) gdn_compose_pairs_kernel(const __grid_con
     for (int i = 0; i < 4; ++i) {
       const int idx = threadIdx.x + i * 256;
       const int xr = idx >> 4, xk = idx & 15;
-      xs[xk][xr] = x[static_cast<int64_t>(row0 + xr) * kDim + k0 + xk];
+      xs[xk][xr] = sum_ld1(x, head_off + static_cast<int64_t>(row0 + xr) * kDim + k0 + xk, bf16);
       const int yk = idx >> 6, yc = idx & 63;
-      ys[yk][yc] = y[static_cast<int64_t>(k0 + yk) * kDim + col0 + yc];
+      ys[yk][yc] = sum_ld1(y, head_off + static_cast<int64_t>(k0 + yk) * kDim + col0 + yc, bf16);
     }
     __syncthreads();
 #pragma unroll
@@ -198,16 +200,16 @@ __global__ void __launch_bounds__(256) gdn_compose_pairs_kernel(const __grid_con
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int64_t o = static_cast<int64_t>(row0 + ty * 4 + i) * kDim + col0 + tx * 4;
+    const int64_t o = head_off + static_cast<int64_t>(row0 + ty * 4 + i) * kDim + col0 + tx * 4;
     float4 r = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
     if (add != nullptr) {
-      const float4 b2 = *reinterpret_cast<const float4*>(add + o);
+      const float4 b2 = sum_ld4(add, o, bf16);
       r.x += b2.x;
       r.y += b2.y;
       r.z += b2.z;
       r.w += b2.w;
     }
-    *reinterpret_cast<float4*>(out + o) = r;
+    sum_st4(out, o, r, bf16);
   }
 }
 
@@ -251,13 +253,15 @@ extern "C" int va_block_copy(const VaPool* pool, int32_t num_layers, int64_t lay
 extern "C" int va_gdn_compose_pairs(const int64_t* a_first, const int64_t* b_first, const int64_t* a_second,
                                     const int64_t* b_second, const int64_t* out_a, const int64_t* out_b,
                                     int32_t num_pairs, int32_t num_v_heads, int32_t head_k_dim,
-                                    int32_t head_v_dim, va_stream_t stream) {
+                                    int32_t head_v_dim, int32_t summary_dtype, va_stream_t stream) {
   if (num_pairs < 0 || num_v_heads <= 0 || num_v_heads > 65535) return VA_ERR_BAD_ARG;
+  if (summary_dtype != VA_SUMMARY_F32 && summary_dtype != VA_SUMMARY_BF16) return VA_ERR_BAD_ARG;
   if (head_k_dim != kDim || head_v_dim != kDim) return VA_ERR_UNSUPPORTED;
   if (num_pairs == 0) return VA_OK;
   if (num_pairs > 32767) return VA_ERR_CAPACITY;
   if (!a_first || !b_first || !a_second || !b_second || !out_a || !out_b) return VA_ERR_BAD_ARG;
-  PairParams p{a_first, b_first, a_second, b_second, out_a, out_b, num_pairs, num_v_heads};
+  PairParams p{a_first, b_first, a_second, b_second, out_a, out_b, num_pairs, num_v_heads,
+               summary_dtype == VA_SUMMARY_BF16 ? 1 : 0};
   gdn_compose_pairs_kernel<<<dim3(4, num_v_heads, num_pairs * 2), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return va_host::note_cuda_error(e);

@@ -33,7 +33,7 @@ int check_pool(const VaPool* pool) {
 
 }  // namespace va_host
 
-extern "C" int va_abi_version(void) { return 4; }
+extern "C" int va_abi_version(void) { return 5; }
 
 extern "C" const char* va_last_cuda_error(void) { return g_last_error; }
 

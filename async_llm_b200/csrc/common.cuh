@@ -116,6 +116,72 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       : "memory");
 }
 
+// ---- GDN block summaries: stored as fp32 or bf16, arithmetic always fp32 ------------------------
+// (the reference's optional bf16 state storage, shared_cache/gdn.py:40-45: values are widened when
+// read and rounded once when a new summary is stored, shared_cache/gdn.py:249-269,
+// shared_cache/gdn_affine.py:113-122)
+__device__ __forceinline__ float4 widen_bf16x4(uint2 r) {
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ uint2 round_bf16x4(float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 r;
+  r.x = *reinterpret_cast<const uint32_t*>(&lo);
+  r.y = *reinterpret_cast<const uint32_t*>(&hi);
+  return r;
+}
+// element i (sum_ld1 / sum_st1) or elements i..i+3, i a multiple of 4 (sum_ld4 / sum_st4)
+__device__ __forceinline__ float sum_ld1(const void* base, int64_t i, bool bf16) {
+  return bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]) : static_cast<const float*>(base)[i];
+}
+__device__ __forceinline__ void sum_st1(void* base, int64_t i, float v, bool bf16) {
+  if (bf16) static_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v);
+  else static_cast<float*>(base)[i] = v;
+}
+__device__ __forceinline__ float4 sum_ld4(const void* base, int64_t i, bool bf16) {
+  if (bf16) return widen_bf16x4(*reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + i));
+  return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + i);
+}
+__device__ __forceinline__ void sum_st4(void* base, int64_t i, float4 v, bool bf16) {
+  if (bf16) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + i) = round_bf16x4(v);
+  else *reinterpret_cast<float4*>(static_cast<float*>(base) + i) = v;
+}
+// the same with the storage type fixed at compile time; Raw is what a row piece occupies in
+// registers while it is in flight
+template <bool kBf16>
+struct SumIO;
+template <>
+struct SumIO<false> {
+  using Raw = float4;
+  static __device__ __forceinline__ Raw ld(const void* base, int64_t i) {
+    return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + i);
+  }
+  static __device__ __forceinline__ Raw ld_stream(const void* base, int64_t i) {
+    return __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(base) + i));
+  }
+  static __device__ __forceinline__ float4 widen(Raw r) { return r; }
+  static __device__ __forceinline__ void st_stream(void* base, int64_t i, float4 v) {
+    __stcs(reinterpret_cast<float4*>(static_cast<float*>(base) + i), v);
+  }
+};
+template <>
+struct SumIO<true> {
+  using Raw = uint2;
+  static __device__ __forceinline__ Raw ld(const void* base, int64_t i) {
+    return *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + i);
+  }
+  static __device__ __forceinline__ Raw ld_stream(const void* base, int64_t i) {
+    return __ldcs(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + i));
+  }
+  static __device__ __forceinline__ float4 widen(Raw r) { return widen_bf16x4(r); }
+  static __device__ __forceinline__ void st_stream(void* base, int64_t i, float4 v) {
+    __stcs(reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + i), round_bf16x4(v));
+  }
+};
+
 // ---- programmatic dependent launch -------------------------------------------------------------
 // A kernel launched with the programmatic-serialization attribute may start while the kernel before
 // it in the stream is still running, once every CTA of that kernel has called

@@ -1,7 +1,8 @@
 // Gated DeltaNet over an ordered block list for sm_100a: fused decode step, initial-state
 // compose, and the token scan of a prefill.  head_k_dim = head_v_dim = 128.
 //
-// A block stores an affine summary (A_hat [H,dk,dk], B_hat [H,dv,dk], fp32) of its tokens:
+// A block stores an affine summary (A_hat [H,dk,dk], B_hat [H,dv,dk]; fp32, or bf16 storage with
+// fp32 arithmetic and one rounding per stored summary) of its tokens:
 // S_out^T = S_in^T A_hat + B_hat (shared_cache/gdn_affine.py:1-24).  A worker's initial state is
 // the fold of its chain, X0 = ((B_0) A_1 + B_1) A_2 + ... (shared_cache/gdn.py:127-180).
 //
@@ -43,6 +44,7 @@ struct StepParams {
   float l2_eps;
   float q_scale;
   int32_t* status;
+  int64_t q_row_stride, k_row_stride, v_row_stride;   // elements between workers' rows
 };
 
 __device__ __forceinline__ float warp_sum(float x) {
@@ -51,12 +53,18 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
-constexpr int kRowsInFlight = 4;   // summary rows a warp has outstanding (4: 4.95 TB/s, 8: 4.71, 1: 3.83 on config 4b)
+// summary rows a warp has outstanding: fp32 rows (512 bytes) 4 (4: 4.95 TB/s, 8: 4.71, 1: 3.83 on
+// config 4b); bf16 rows are half as long, so twice as many keep the same bytes in flight
+template <bool kBf16>
+constexpr int kRowsInFlight = kBf16 ? 8 : 4;
 
 // grid (Hv, W), 256 threads.  Vectors live in shared memory as fp32.
 // (5 CTAs per SM, 48 registers: +8 % over the 4 CTAs that the unconstrained 60 registers allow; 6 and 8
 // CTAs spill more than they gain)
+template <bool kBf16>
 __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant__ StepParams p) {
+  using IO = SumIO<kBf16>;
+  constexpr int RF = kRowsInFlight<kBf16>;
   __shared__ __align__(16) float kn[kD];   // l2-normalised key
   __shared__ __align__(16) float qn[kD];   // l2-normalised, scaled query
   __shared__ __align__(16) float vv[kD];
@@ -75,10 +83,9 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
   // ---- load and normalise the token's vectors
   float kx = 0.f, qx = 0.f;
   if (tid < kD) {
-    const int64_t qk_off = (static_cast<int64_t>(w) * p.num_k_heads + hk) * kD + tid;
-    kx = __bfloat162float(p.k[qk_off]);
-    qx = __bfloat162float(p.q[qk_off]);
-    vv[tid] = __bfloat162float(p.v[(static_cast<int64_t>(w) * p.num_v_heads + h) * kD + tid]);
+    kx = __bfloat162float(p.k[static_cast<int64_t>(w) * p.k_row_stride + hk * kD + tid]);
+    qx = __bfloat162float(p.q[static_cast<int64_t>(w) * p.q_row_stride + hk * kD + tid]);
+    vv[tid] = __bfloat162float(p.v[static_cast<int64_t>(w) * p.v_row_stride + h * kD + tid]);
     yk[tid] = 0.f;
     yq[tid] = 0.f;
   }
@@ -109,37 +116,38 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
 
   // ---- phase 1: the write block's summary, one row per warp pass: dot with k and q, rank-1
   //      update, write the fresh row.  rows 0..127 are A_hat, 128..255 are B_hat.
-  const float* ra = reinterpret_cast<const float*>(p.read_a[w]);
-  const float* rb = reinterpret_cast<const float*>(p.read_b[w]);
-  float* wa = reinterpret_cast<float*>(p.write_a[w]);
-  float* wb = reinterpret_cast<float*>(p.write_b[w]);
+  const void* ra = reinterpret_cast<const void*>(p.read_a[w]);
+  const void* rb = reinterpret_cast<const void*>(p.read_b[w]);
+  void* wa = reinterpret_cast<void*>(p.write_a[w]);
+  void* wb = reinterpret_cast<void*>(p.write_b[w]);
   const int64_t head_off = static_cast<int64_t>(h) * kD * kD;
-  // A warp takes kRowsInFlight consecutive rows per pass and fetches all of them before it reduces the first:
+  // A warp takes RF consecutive rows per pass and fetches all of them before it reduces the first:
   // with one row in flight per warp the SM had too few bytes outstanding to cover the HBM latency.
-  for (int r0 = warp * kRowsInFlight; r0 < 2 * kD; r0 += 8 * kRowsInFlight) {
-    float4 xr[kRowsInFlight];
+  for (int r0 = warp * RF; r0 < 2 * kD; r0 += 8 * RF) {
+    typename IO::Raw xr[RF];
 #pragma unroll
-    for (int u = 0; u < kRowsInFlight; ++u) {
+    for (int u = 0; u < RF; ++u) {
       const int r = r0 + u;
       const bool is_b = r >= kD;
       const int row = is_b ? r - kD : r;
-      const float* src = is_b ? rb : ra;
-      if (src != nullptr) {
-        // read once (and rewritten below): streaming loads and stores keep the chain blocks, which
-        // every worker re-reads, in L2
-        xr[u] = __ldcs(reinterpret_cast<const float4*>(src + head_off + static_cast<int64_t>(row) * kD + lane * 4));
-      } else {
-        // no summary yet: A_hat = I, B_hat = 0
-        xr[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!is_b && (row >> 2) == lane) reinterpret_cast<float*>(&xr[u])[row & 3] = 1.f;
-      }
+      const void* src = is_b ? rb : ra;
+      // read once (and rewritten below): streaming loads and stores keep the chain blocks, which
+      // every worker re-reads, in L2
+      if (src != nullptr) xr[u] = IO::ld_stream(src, head_off + static_cast<int64_t>(row) * kD + lane * 4);
     }
 #pragma unroll
-    for (int u = 0; u < kRowsInFlight; ++u) {
+    for (int u = 0; u < RF; ++u) {
       const int r = r0 + u;
       const bool is_b = r >= kD;
       const int row = is_b ? r - kD : r;
-      const float4 x = xr[u];
+      float4 x;
+      if ((is_b ? rb : ra) != nullptr) {
+        x = IO::widen(xr[u]);
+      } else {
+        // no summary yet: A_hat = I, B_hat = 0
+        x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!is_b && (row >> 2) == lane) reinterpret_cast<float*>(&x)[row & 3] = 1.f;
+      }
       const float dk_ = warp_sum(x.x * k4.x + x.y * k4.y + x.z * k4.z + x.w * k4.w);
       const float dq_ = warp_sum(x.x * q4.x + x.y * q4.y + x.z * q4.z + x.w * q4.w);
       // A' = alpha A - (alpha beta (A k)) k^T ;  B' = alpha B - (alpha beta (B k)) k^T + (beta v) k^T
@@ -156,9 +164,8 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
         y.z = __fadd_rn(y.z, __fmul_rn(t2, k4.z));
         y.w = __fadd_rn(y.w, __fmul_rn(t2, k4.w));
       }
-      float* dst = is_b ? wb : wa;
-      if (dst != nullptr)
-        __stcs(reinterpret_cast<float4*>(dst + head_off + static_cast<int64_t>(row) * kD + lane * 4), y);
+      void* dst = is_b ? wb : wa;
+      if (dst != nullptr) IO::st_stream(dst, head_off + static_cast<int64_t>(row) * kD + lane * 4, y);
       if (lane == 0) {
         if (is_b) {
           // contribution of the write block if it closes the chain (used in phase 2)
@@ -185,8 +192,8 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
   int cur = 0;  // which of uk[cur]/uq[cur] holds the current vectors
   bool fresh = true;  // current vectors are still the token's own k / q
   for (int j = last; j >= 0; --j) {
-    const float* bj = reinterpret_cast<const float*>(p.chain_b[static_cast<int64_t>(w) * p.depth + j]);
-    const float* aj = reinterpret_cast<const float*>(p.chain_a[static_cast<int64_t>(w) * p.depth + j]);
+    const void* bj = reinterpret_cast<const void*>(p.chain_b[static_cast<int64_t>(w) * p.depth + j]);
+    const void* aj = reinterpret_cast<const void*>(p.chain_a[static_cast<int64_t>(w) * p.depth + j]);
     if (bj == nullptr) continue;
     bool earlier = false;
     for (int i = j - 1; i >= 0; --i) earlier = earlier || p.chain_b[static_cast<int64_t>(w) * p.depth + i] != 0;
@@ -213,22 +220,21 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
     const int nxt = fresh ? 0 : cur ^ 1;
     __syncthreads();  // everyone has read uk[cur] before uk[nxt] (== scratch) is overwritten
     const int n_rows = earlier ? 2 * kD : kD;
-    for (int r0 = warp * kRowsInFlight; r0 < n_rows; r0 += 8 * kRowsInFlight) {   // as in phase 1
-      float4 xr[kRowsInFlight];
+    for (int r0 = warp * RF; r0 < n_rows; r0 += 8 * RF) {   // as in phase 1
+      typename IO::Raw xr[RF];
 #pragma unroll
-      for (int u = 0; u < kRowsInFlight; ++u) {
+      for (int u = 0; u < RF; ++u) {
         const int r = r0 + u;
         const bool is_a = r >= kD;
         const int row = is_a ? r - kD : r;
-        const float* src = is_a ? aj : bj;
-        xr[u] = *reinterpret_cast<const float4*>(src + head_off + static_cast<int64_t>(row) * kD + lane * 4);
+        xr[u] = IO::ld(is_a ? aj : bj, head_off + static_cast<int64_t>(row) * kD + lane * 4);
       }
 #pragma unroll
-      for (int u = 0; u < kRowsInFlight; ++u) {
+      for (int u = 0; u < RF; ++u) {
         const int r = r0 + u;
         const bool is_a = r >= kD;
         const int row = is_a ? r - kD : r;
-        const float4 x = xr[u];
+        const float4 x = IO::widen(xr[u]);
         const float dk_ = warp_sum(x.x * ck.x + x.y * ck.y + x.z * ck.z + x.w * ck.w);
         const float dq_ = warp_sum(x.x * cq.x + x.y * cq.y + x.z * cq.z + x.w * cq.w);
         if (lane == 0) {
@@ -272,7 +278,9 @@ struct ComposeParams {
 
 // grid (H, W), 256 threads; X (dv x dk) and its successor in shared memory (2 x 64 KB).
 // Thread (ty, tx) owns the 8x8 block rows 8ty.., cols 8tx.. of X A_j + B_j.
+template <bool kBf16>
 __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant__ ComposeParams p) {
+  using IO = SumIO<kBf16>;
   extern __shared__ __align__(16) float xs[];  // 2 * 128 * 128
   const int h = blockIdx.x;
   const int w = blockIdx.y;
@@ -284,13 +292,13 @@ __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant_
   float* nxt = xs + kD * kD;
   bool have = false;
   for (int j = 0; j < p.depth; ++j) {
-    const float* aj = reinterpret_cast<const float*>(p.chain_a[static_cast<int64_t>(w) * p.depth + j]);
-    const float* bj = reinterpret_cast<const float*>(p.chain_b[static_cast<int64_t>(w) * p.depth + j]);
+    const void* aj = reinterpret_cast<const void*>(p.chain_a[static_cast<int64_t>(w) * p.depth + j]);
+    const void* bj = reinterpret_cast<const void*>(p.chain_b[static_cast<int64_t>(w) * p.depth + j]);
     if (bj == nullptr || aj == nullptr) continue;
     if (!have) {
       // the fold starts at the first block with a summary: X = B_j
       for (int i = tid * 4; i < kD * kD; i += 256 * 4)
-        *reinterpret_cast<float4*>(cur + i) = *reinterpret_cast<const float4*>(bj + head_off + i);
+        *reinterpret_cast<float4*>(cur + i) = IO::widen(IO::ld(bj, head_off + i));
       have = true;
       __syncthreads();
       continue;
@@ -301,8 +309,8 @@ __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant_
 #pragma unroll
       for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
     for (int i = 0; i < kD; ++i) {
-      const float4 a0 = *reinterpret_cast<const float4*>(aj + head_off + static_cast<int64_t>(i) * kD + tx * 8);
-      const float4 a1 = *reinterpret_cast<const float4*>(aj + head_off + static_cast<int64_t>(i) * kD + tx * 8 + 4);
+      const float4 a0 = IO::widen(IO::ld(aj, head_off + static_cast<int64_t>(i) * kD + tx * 8));
+      const float4 a1 = IO::widen(IO::ld(aj, head_off + static_cast<int64_t>(i) * kD + tx * 8 + 4));
       const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
@@ -313,9 +321,9 @@ __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant_
     }
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-      const float* brow = bj + head_off + static_cast<int64_t>(ty * 8 + r) * kD + tx * 8;
-      const float4 b0 = *reinterpret_cast<const float4*>(brow);
-      const float4 b1 = *reinterpret_cast<const float4*>(brow + 4);
+      const int64_t brow = head_off + static_cast<int64_t>(ty * 8 + r) * kD + tx * 8;
+      const float4 b0 = IO::widen(IO::ld(bj, brow));
+      const float4 b1 = IO::widen(IO::ld(bj, brow + 4));
       float* dst = nxt + (ty * 8 + r) * kD + tx * 8;
       *reinterpret_cast<float4*>(dst) =
           make_float4(acc[r][0] + b0.x, acc[r][1] + b0.y, acc[r][2] + b0.z, acc[r][3] + b0.w);
@@ -365,6 +373,7 @@ struct ScanParams {
   float* s_eg;           // [Hv][N] e^gc
   float* s_ed;           // [Hv][N] e^(gc_last - gc)
   int64_t num_tokens;
+  int32_t summary_bf16;  // init_a/init_b/write_a/write_b name bf16 tensors (fp32 otherwise)
 };
 
 constexpr int kScanTokens = 16;  // tokens staged per pass
@@ -402,12 +411,12 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const __grid_constant__ S
       for (int i = 0; i < kD; ++i) col[i] = 0.f;
     }
   } else {
-    const float* init = reinterpret_cast<const float*>(part == 1 ? p.init_a[r] : p.init_b[r]);
+    const void* init = reinterpret_cast<const void*>(part == 1 ? p.init_a[r] : p.init_b[r]);
     if (init != nullptr) {
-      const float4* row = reinterpret_cast<const float4*>(init + head_off + static_cast<int64_t>(c) * kD);
+      const int64_t row = head_off + static_cast<int64_t>(c) * kD;
 #pragma unroll
       for (int i = 0; i < kD / 4; ++i) {
-        const float4 x = row[i];
+        const float4 x = sum_ld4(init, row + 4 * i, p.summary_bf16 != 0);
         col[4 * i] = x.x;
         col[4 * i + 1] = x.y;
         col[4 * i + 2] = x.z;
@@ -511,12 +520,13 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const __grid_constant__ S
       for (int i = 0; i < kD; ++i) dst[i * kD + c] = col[i];
     }
   } else {
-    float* dst = reinterpret_cast<float*>(part == 1 ? p.write_a[r] : p.write_b[r]);
+    void* dst = reinterpret_cast<void*>(part == 1 ? p.write_a[r] : p.write_b[r]);
     if (dst != nullptr) {
-      float4* row = reinterpret_cast<float4*>(dst + head_off + static_cast<int64_t>(c) * kD);
+      const int64_t row = head_off + static_cast<int64_t>(c) * kD;
 #pragma unroll
       for (int i = 0; i < kD / 4; ++i)
-        row[i] = make_float4(col[4 * i], col[4 * i + 1], col[4 * i + 2], col[4 * i + 3]);
+        sum_st4(dst, row + 4 * i, make_float4(col[4 * i], col[4 * i + 1], col[4 * i + 2], col[4 * i + 3]),
+                p.summary_bf16 != 0);
     }
   }
 }
@@ -862,13 +872,18 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
 
   float acc[2][16][4];
   {
-    const float* src = nullptr;
+    const void* src = nullptr;   // part 0: fp32 state; parts 1, 2: a summary in its storage type
+    int64_t src_off = 0;
     bool transposed = false;
+    const bool sum_bf16 = part != 0 && p.summary_bf16 != 0;
     if (part == 0) {
-      if (p.state0 != nullptr) src = p.state0 + (static_cast<int64_t>(r) * p.num_v_heads + h) * kD * kD;
+      if (p.state0 != nullptr) {
+        src = p.state0;
+        src_off = (static_cast<int64_t>(r) * p.num_v_heads + h) * kD * kD;
+      }
     } else {
-      const float* init = reinterpret_cast<const float*>(part == 1 ? p.init_a[r] : p.init_b[r]);
-      if (init != nullptr) src = init + head_off;
+      src = reinterpret_cast<const void*>(part == 1 ? p.init_a[r] : p.init_b[r]);
+      src_off = head_off;
       transposed = true;
     }
 #pragma unroll
@@ -880,7 +895,7 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
           const int row = 32 * warp + 16 * mt + g + (e >> 1) * 8;
           const int col = 8 * nt + 2 * t + (e & 1);
           float x = (part == 1 && row == col) ? 1.f : 0.f;
-          if (src != nullptr) x = transposed ? src[col * kD + row] : src[row * kD + col];
+          if (src != nullptr) x = sum_ld1(src, src_off + (transposed ? col * kD + row : row * kD + col), sum_bf16);
           acc[mt][nt][e] = x;
         }
       }
@@ -1059,13 +1074,18 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
 
   // ---- hand the state off
   {
-    float* dst = nullptr;
+    void* dst = nullptr;
+    int64_t dst_off = 0;
     bool transposed = false;
+    const bool sum_bf16 = part != 0 && p.summary_bf16 != 0;
     if (part == 0) {
-      if (p.final_state != nullptr) dst = p.final_state + (static_cast<int64_t>(r) * p.num_v_heads + h) * kD * kD;
+      if (p.final_state != nullptr) {
+        dst = p.final_state;
+        dst_off = (static_cast<int64_t>(r) * p.num_v_heads + h) * kD * kD;
+      }
     } else {
-      float* w = reinterpret_cast<float*>(part == 1 ? p.write_a[r] : p.write_b[r]);
-      if (w != nullptr) dst = w + head_off;
+      dst = reinterpret_cast<void*>(part == 1 ? p.write_a[r] : p.write_b[r]);
+      dst_off = head_off;
       transposed = true;
     }
     if (dst != nullptr) {
@@ -1077,8 +1097,7 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
           for (int e = 0; e < 4; ++e) {
             const int row = 32 * warp + 16 * mt + g + (e >> 1) * 8;
             const int col = 8 * nt + 2 * t + (e & 1);
-            if (transposed) dst[col * kD + row] = acc[mt][nt][e];
-            else dst[row * kD + col] = acc[mt][nt][e];
+            sum_st1(dst, dst_off + (transposed ? col * kD + row : row * kD + col), acc[mt][nt][e], sum_bf16);
           }
         }
       }
@@ -1124,8 +1143,20 @@ extern "C" int va_gdn_step(const VaGdnStep* a, va_stream_t stream) {
   p.l2_eps = a->l2_eps;
   p.q_scale = a->q_scale;
   p.status = a->status;
+  // rows of q / k / v may lie inside wider rows (the conv output [q | k | v] of a layer): strides
+  // in elements, 0 = dense
+  p.q_row_stride = a->q_row_stride > 0 ? a->q_row_stride : static_cast<int64_t>(a->num_k_heads) * kD;
+  p.k_row_stride = a->k_row_stride > 0 ? a->k_row_stride : static_cast<int64_t>(a->num_k_heads) * kD;
+  p.v_row_stride = a->v_row_stride > 0 ? a->v_row_stride : static_cast<int64_t>(a->num_v_heads) * kD;
+  if (p.q_row_stride < static_cast<int64_t>(a->num_k_heads) * kD || p.k_row_stride < static_cast<int64_t>(a->num_k_heads) * kD ||
+      p.v_row_stride < static_cast<int64_t>(a->num_v_heads) * kD)
+    return VA_ERR_BAD_ARG;
+  if (a->summary_dtype != VA_SUMMARY_F32 && a->summary_dtype != VA_SUMMARY_BF16) return VA_ERR_BAD_ARG;
   dim3 grid(a->num_v_heads, a->num_workers);
-  gdn_step_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (a->summary_dtype == VA_SUMMARY_BF16)
+    gdn_step_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    gdn_step_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return va_host::note_cuda_error(e);
   return VA_OK;
@@ -1133,9 +1164,10 @@ extern "C" int va_gdn_step(const VaGdnStep* a, va_stream_t stream) {
 
 extern "C" int va_gdn_compose(const int64_t* chain_a, const int64_t* chain_b, float* state,
                               int32_t num_workers, int32_t depth, int32_t num_heads, int32_t head_k_dim,
-                              int32_t head_v_dim, va_stream_t stream) {
+                              int32_t head_v_dim, int32_t summary_dtype, va_stream_t stream) {
   int rc = check_gdn_dims(num_heads, num_heads, head_k_dim, head_v_dim);
   if (rc != VA_OK) return rc;
+  if (summary_dtype != VA_SUMMARY_F32 && summary_dtype != VA_SUMMARY_BF16) return VA_ERR_BAD_ARG;
   if (num_workers < 0 || depth < 0) return VA_ERR_BAD_ARG;
   if (num_workers == 0) return VA_OK;
   if (state == nullptr || (depth > 0 && (chain_a == nullptr || chain_b == nullptr))) return VA_ERR_BAD_ARG;
@@ -1147,10 +1179,11 @@ extern "C" int va_gdn_compose(const int64_t* chain_a, const int64_t* chain_b, fl
   p.depth = depth;
   p.num_heads = num_heads;
   const int smem = 2 * kD * kD * static_cast<int>(sizeof(float));
-  cudaError_t e = cudaFuncSetAttribute(gdn_compose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  auto kernel = summary_dtype == VA_SUMMARY_BF16 ? gdn_compose_kernel<true> : gdn_compose_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return va_host::note_cuda_error(e);
   dim3 grid(num_heads, num_workers);
-  gdn_compose_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return va_host::note_cuda_error(e);
   return VA_OK;
@@ -1197,6 +1230,8 @@ extern "C" int va_gdn_prefill(const VaGdnPrefill* a, va_stream_t stream) {
   p.s_k = p.s_q = p.s_w = p.s_u = p.s_p = nullptr;
   p.s_eg = p.s_ed = nullptr;
   p.num_tokens = 0;
+  if (a->summary_dtype != VA_SUMMARY_F32 && a->summary_dtype != VA_SUMMARY_BF16) return VA_ERR_BAD_ARG;
+  p.summary_bf16 = a->summary_dtype == VA_SUMMARY_BF16;
   dim3 grid(3, a->num_v_heads, a->num_requests);
   cudaError_t e;
   if (a->engine == VA_GDN_ENGINE_CHUNK && a->scratch != nullptr) {

@@ -22,8 +22,9 @@ struct PreParams {
   int64_t qkv_row_stride;
   const __nv_bfloat16* prior_conv;   // [W, conv_dim, k] or null (zeros)
   const __nv_bfloat16* conv_weight;  // [conv_dim, k]
-  const __nv_bfloat16* a;            // [W, Hv]
-  const __nv_bfloat16* b;            // [W, Hv]
+  const __nv_bfloat16* a;            // [W, Hv] rows a_row_stride elements apart
+  const __nv_bfloat16* b;            // [W, Hv] rows b_row_stride elements apart
+  int64_t a_row_stride, b_row_stride;
   const float* a_log;                // [Hv]
   const float* dt_bias;              // [Hv]
   __nv_bfloat16* qkv_out;            // [W, conv_dim]
@@ -76,25 +77,29 @@ __global__ void __launch_bounds__(256) gdn_decode_pre_kernel(const __grid_consta
   if (blockIdx.y != 0) return;
   for (int h = threadIdx.x; h < p.num_v_heads; h += blockDim.x) {
     const int64_t i = static_cast<int64_t>(w) * p.num_v_heads + h;
-    const float bv = __bfloat162float(p.b[i]);
+    const float bv = __bfloat162float(p.b[static_cast<int64_t>(w) * p.b_row_stride + h]);
     const __nv_bfloat16 beta = __float2bfloat16_rn(1.0f / (1.0f + expf(-bv)));
     p.beta_out[i] = beta;
     if (p.beta_f32_out != nullptr) p.beta_f32_out[i] = __bfloat162float(beta);
-    const float z = __fadd_rn(__bfloat162float(p.a[i]), p.dt_bias[h]);
+    const float z = __fadd_rn(__bfloat162float(p.a[static_cast<int64_t>(w) * p.a_row_stride + h]), p.dt_bias[h]);
     const float sp = z > 20.0f ? z : log1pf(expf(z));   // softplus, threshold 20
     p.g_out[i] = __fmul_rn(-expf(p.a_log[h]), sp);
   }
 }
 
-// One warp per row of `dim` elements (dim a multiple of 32, at most 1024).
+// One warp per row of `dim` elements (dim a multiple of 32, at most 1024).  The gate rows of one
+// token (rows_per_token of them, `dim` apart) may lie inside a wider projection row: tokens are
+// gate_token_stride elements apart.
 __global__ void __launch_bounds__(256) gdn_gated_rmsnorm_kernel(const __nv_bfloat16* x, const __nv_bfloat16* gate,
                                                                 const float* weight, __nv_bfloat16* out,
-                                                                int64_t rows, int dim, float eps) {
+                                                                int64_t rows, int dim, float eps, int rows_per_token,
+                                                                int64_t gate_token_stride) {
   const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const __nv_bfloat16* xr = x + row * dim;
-  const __nv_bfloat16* gr = gate + row * dim;
+  const int64_t tok = row / rows_per_token;
+  const __nv_bfloat16* gr = gate + tok * gate_token_stride + (row - tok * rows_per_token) * dim;
   const int per = dim >> 5;
   float v[32];
   float ss = 0.0f;
@@ -197,6 +202,9 @@ extern "C" int va_gdn_decode_pre(const VaGdnDecodePre* a, va_stream_t stream) {
   p.conv_weight = static_cast<const __nv_bfloat16*>(a->conv_weight);
   p.a = static_cast<const __nv_bfloat16*>(a->a);
   p.b = static_cast<const __nv_bfloat16*>(a->b);
+  p.a_row_stride = a->a_row_stride > 0 ? a->a_row_stride : a->num_v_heads;
+  p.b_row_stride = a->b_row_stride > 0 ? a->b_row_stride : a->num_v_heads;
+  if (p.a_row_stride < a->num_v_heads || p.b_row_stride < a->num_v_heads) return VA_ERR_BAD_ARG;
   p.a_log = a->a_log;
   p.dt_bias = a->dt_bias;
   p.qkv_out = static_cast<__nv_bfloat16*>(a->qkv_out);
@@ -222,15 +230,21 @@ extern "C" int va_gdn_decode_pre(const VaGdnDecodePre* a, va_stream_t stream) {
 }
 
 extern "C" int va_gdn_gated_rmsnorm(const void* x, const void* gate, const float* weight, void* out,
-                                    int64_t rows, int32_t dim, float eps, va_stream_t stream) {
+                                    int64_t rows, int32_t dim, float eps, int32_t rows_per_token,
+                                    int64_t gate_token_stride, va_stream_t stream) {
   if (rows < 0 || dim <= 0 || (dim & 31) || dim > 1024) return VA_ERR_BAD_ARG;
   if (rows == 0) return VA_OK;
   if (!x || !gate || !weight || !out) return VA_ERR_BAD_ARG;
+  if (rows_per_token <= 0) {   // dense gate rows
+    rows_per_token = 1;
+    gate_token_stride = dim;
+  }
+  if (gate_token_stride < static_cast<int64_t>(rows_per_token) * dim || rows % rows_per_token != 0) return VA_ERR_BAD_ARG;
   const int64_t blocks = (rows + 7) / 8;
   if (blocks > 0x7fffffffLL) return VA_ERR_CAPACITY;
   gdn_gated_rmsnorm_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gate), weight,
-      static_cast<__nv_bfloat16*>(out), rows, dim, eps);
+      static_cast<__nv_bfloat16*>(out), rows, dim, eps, rows_per_token, gate_token_stride);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return va_host::note_cuda_error(e);
   return VA_OK;

@@ -74,12 +74,26 @@ def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     if x.dtype != torch.bfloat16:
         raise NotImplementedError("the GDN layer kernels take bfloat16 activations")
     dim = x.shape[-1]
-    xc, gc = x.contiguous(), gate.to(torch.bfloat16).contiguous()
-    assert gc.shape == xc.shape
+    xc = x.contiguous()
+    assert gate.shape == xc.shape
+    # the gate may be a slice of a wider projection output ``[tokens, ..., dim]``: its rows are read
+    # where they lie when everything but the token dimension is dense
+    rows_per_token, token_stride = 0, 0
+    gc = gate
+    inner = 1
+    dense_inner = gate.dtype == torch.bfloat16 and gate.dim() >= 2
+    for d in range(gate.dim() - 1, 0, -1):
+        dense_inner = dense_inner and gate.stride(d) == inner
+        inner *= gate.shape[d]
+    if dense_inner and gate.stride(0) >= inner:
+        rows_per_token, token_stride = inner // dim, gate.stride(0)
+    else:
+        gc = gate.to(torch.bfloat16).contiguous()
     w = weight.to(device=x.device, dtype=torch.float32).contiguous()
     out = torch.empty_like(xc)
     rc = _lib.lib().va_gdn_gated_rmsnorm(xc.data_ptr(), gc.data_ptr(), w.data_ptr(), out.data_ptr(),
-                                         xc.numel() // dim, dim, float(eps), _lib.stream_ptr())
+                                         xc.numel() // dim, dim, float(eps), rows_per_token, token_stride,
+                                         _lib.stream_ptr())
     _lib.check(rc, "va_gdn_gated_rmsnorm")
     return out
 

@@ -145,10 +145,11 @@ class SharedCacheGDN:
         num_k_heads: Optional[int] = None,
         prefill_engine: Optional[str] = None,
     ) -> None:
-        if state_dtype != torch.float32:
-            if state_dtype == torch.bfloat16:
-                raise NotImplementedError("bfloat16 GDN summaries are not built into the B200 kernels")
+        # summaries are stored in ``state_dtype``; the kernels widen them when read, work in fp32 and
+        # round once when a new summary is stored (minisgl/shared_cache/gdn.py:40-45,249-269)
+        if state_dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("Shared GDN state dtype must be float32 or bfloat16")
+        self._summary_code = _lib.summary_code(state_dtype)
         # fused prefill: "chunk" = 64-token chunks on the tensor cores (bf16 operands, fp32 state),
         # "scan" = token-by-token fp32 recurrence (also what capture_token_affines always runs)
         self.prefill_engine = prefill_engine or os.environ.get("VIEWATTN_GDN_ENGINE", "chunk")
@@ -199,8 +200,8 @@ class SharedCacheGDN:
         H, dk, dv = self.num_heads, self.head_k_dim, self.head_v_dim
         if tuple(a.shape) != (1, H, dk, dk) or tuple(b.shape) != (1, H, dv, dk):
             raise ValueError(f"Unexpected GDN state shape {tuple(a.shape)} / {tuple(b.shape)}")
-        a2 = a.to(device=self.device, dtype=torch.float32).contiguous()
-        b2 = b.to(device=self.device, dtype=torch.float32).contiguous()
+        a2 = a.to(device=self.device, dtype=self.state_dtype).contiguous()
+        b2 = b.to(device=self.device, dtype=self.state_dtype).contiguous()
         keep += [a2, b2]
         return a2.data_ptr(), b2.data_ptr()
 
@@ -210,12 +211,12 @@ class SharedCacheGDN:
         the same addresses behind its StateDict, minisgl/shared_cache/gdn_state.py:15-58)."""
         rev = getattr(block, "_gdn_revision", None)
         c = getattr(block, "_gdn_ptr_cache", None) if rev is not None else None
-        if c is None or c[0] != rev or c[1] != self.device or c[2].shape[0] < layers:
+        if c is None or c[0] != rev or c[1] != (self.device, self.state_dtype) or c[2].shape[0] < layers:
             held: list = []
             ptrs = np.zeros((layers, 2), np.int64)
             for layer in range(layers):
                 ptrs[layer] = self._pair_ptrs(block, layer, held)
-            c = (rev, self.device, ptrs, held)
+            c = (rev, (self.device, self.state_dtype), ptrs, held)
             if rev is not None:   # a block without a revision counter (the reference's own class) is re-read
                 block._gdn_ptr_cache = c
         keep.append(c[3])
@@ -299,20 +300,21 @@ class SharedCacheGDN:
             steps = np.arange(layers, dtype=np.int64)
             if dk == dv:
                 # A_hat and B_hat of all layers of one worker in one allocation: [2 * layers, 1, H, d, d]
-                out_a = [torch.empty(2 * layers, 1, H, dk, dk, dtype=torch.float32, device=self.device)
+                out_a = [torch.empty(2 * layers, 1, H, dk, dk, dtype=self.state_dtype, device=self.device)
                          for _ in targets]
                 out_b = None
                 base = np.fromiter((t.data_ptr() for t in out_a), np.int64, W)
-                stride = H * dk * dk * 4
+                stride = H * dk * dk * out_a[0].element_size() if W else 0
                 tab[ROW_WRITE_A, :, :, 0] = base[None, :] + steps[:, None] * stride
                 tab[ROW_WRITE_B, :, :, 0] = base[None, :] + (layers + steps[:, None]) * stride
             else:
-                out_a = [torch.empty(layers, 1, H, dk, dk, dtype=torch.float32, device=self.device) for _ in targets]
-                out_b = [torch.empty(layers, 1, H, dv, dk, dtype=torch.float32, device=self.device) for _ in targets]
+                out_a = [torch.empty(layers, 1, H, dk, dk, dtype=self.state_dtype, device=self.device) for _ in targets]
+                out_b = [torch.empty(layers, 1, H, dv, dk, dtype=self.state_dtype, device=self.device) for _ in targets]
+                esz = out_a[0].element_size() if W else 0
                 tab[ROW_WRITE_A, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_a), np.int64, W)[None, :]
-                                             + steps[:, None] * (out_a[0].stride(0) * 4))
+                                             + steps[:, None] * (H * dk * dk * esz))
                 tab[ROW_WRITE_B, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_b), np.int64, W)[None, :]
-                                             + steps[:, None] * (out_b[0].stride(0) * 4))
+                                             + steps[:, None] * (H * dv * dk * esz))
         if buffers is not None:
             buffers.load(tab)
             dev, rw, run_W, run_depth = buffers.tab, buffers.rw, buffers.workers, buffers.depth
@@ -420,12 +422,15 @@ class SharedCacheGDN:
             raise RuntimeError("the GDN step kernel needs CUDA tensors: there is no CPU fallback")
         st = self._step
         W = st["W"]
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        # rows of q / k / v are read where they lie (slices of a layer's [q | k | v] conv output)
+        q, k, v = (t if (t.stride(2) == 1 and t.stride(1) == t.shape[2]) else t.contiguous() for t in (q, k, v))
         g32, b32 = g.float().contiguous(), beta.float().contiguous()
         out = torch.empty(W, self.num_heads, self.head_v_dim, dtype=q.dtype, device=q.device)
         tab = st["tab"]
         a = _lib.VaGdnStep()
         a.q, a.k, a.v, a.g, a.beta, a.out = (t.data_ptr() for t in (q, k, v, g32, b32, out))
+        a.q_row_stride, a.k_row_stride, a.v_row_stride = q.stride(0), k.stride(0), v.stride(0)
+        a.summary_dtype = self._summary_code
         a.chain_a = tab[0, lin_idx].data_ptr()
         a.chain_b = tab[1, lin_idx].data_ptr()
         row = st["rw"].data_ptr() + lin_idx * 6 * W * 8                # [6, W] int64 rows of this layer
@@ -460,7 +465,9 @@ class SharedCacheGDN:
         weight = conv_weight.reshape(self.conv_dim, -1).to(torch.bfloat16).contiguous()
         assert weight.shape[1] == self.conv_kernel
         Hv = self.num_heads
-        a2, b2 = a.reshape(W, Hv).to(torch.bfloat16).contiguous(), b.reshape(W, Hv).to(torch.bfloat16).contiguous()
+        # a / b are read where they lie (columns of the fused input projection)
+        a2, b2 = (t if (t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape == (W, Hv) and t.stride(1) == 1)
+                  else t.reshape(W, Hv).to(torch.bfloat16).contiguous() for t in (a, b))
         a_log = A_log.to(device=self.device, dtype=torch.float32).contiguous()
         bias = dt_bias.to(device=self.device, dtype=torch.float32).contiguous()
         qkv_out = torch.empty(W, self.conv_dim, dtype=torch.bfloat16, device=self.device)
@@ -473,6 +480,7 @@ class SharedCacheGDN:
         args.prior_conv, args.conv_out = None, None
         args.prior_conv_ptrs, args.conv_out_ptrs = row + 2 * W * 8, row + 5 * W * 8
         args.conv_weight, args.a, args.b = weight.data_ptr(), a2.data_ptr(), b2.data_ptr()
+        args.a_row_stride, args.b_row_stride = a2.stride(0), b2.stride(0)
         args.a_log, args.dt_bias = a_log.data_ptr(), bias.data_ptr()
         args.qkv_out, args.beta_out, args.beta_f32_out, args.g_out = (qkv_out.data_ptr(), beta16.data_ptr(),
                                                                       beta.data_ptr(), g.data_ptr())
@@ -495,7 +503,7 @@ class SharedCacheGDN:
                             device=self.device)
         rc = _lib.lib().va_gdn_compose(st["tab"][0, lin_idx].data_ptr(), st["tab"][1, lin_idx].data_ptr(),
                                        state.data_ptr(), W, st["depth"], self.num_heads,
-                                       self.head_k_dim, self.head_v_dim, _lib.stream_ptr())
+                                       self.head_k_dim, self.head_v_dim, self._summary_code, _lib.stream_ptr())
         _lib.check(rc, "va_gdn_compose")
         if st is not self._step:
             ev = torch.cuda.Event()
@@ -537,8 +545,8 @@ class SharedCacheGDN:
         keep: list = []
         init = np.zeros((4, W), dtype=np.int64)
         H_, dv = self.num_heads, self.head_v_dim
-        out_a = [torch.empty(1, H_, dk, dk, dtype=torch.float32, device=self.device) for _ in targets]
-        out_b = [torch.empty(1, H_, dv, dk, dtype=torch.float32, device=self.device) for _ in targets]
+        out_a = [torch.empty(1, H_, dk, dk, dtype=self.state_dtype, device=self.device) for _ in targets]
+        out_b = [torch.empty(1, H_, dv, dk, dtype=self.state_dtype, device=self.device) for _ in targets]
         for w, target in enumerate(targets):
             init[0, w], init[1, w] = self._pair_ptrs(target, lin_idx, keep)
             init[2, w], init[3, w] = out_a[w].data_ptr(), out_b[w].data_ptr()
@@ -605,6 +613,7 @@ class SharedCacheGDN:
         a.head_k_dim, a.head_v_dim = self.head_k_dim, self.head_v_dim
         a.l2_eps, a.q_scale = eps, self.head_k_dim ** -0.5
         a.engine = GDN_ENGINES[engine]
+        a.summary_dtype = self._summary_code
         a.num_tokens = N
         a.max_segment_tokens = (int(max(segments)) if len(segments) else 0) if buffers is None else N
         if engine == "chunk" and buffers is not None:
@@ -684,7 +693,7 @@ class SharedCacheGDN:
                                  dtype=torch.float32, device=self.device)
             rc = _lib.lib().va_gdn_compose(st["tab"][0, lin_idx].data_ptr(), st["tab"][1, lin_idx].data_ptr(),
                                            state0.data_ptr(), st["W"], st["depth"], self.num_heads,
-                                           self.head_k_dim, self.head_v_dim, _lib.stream_ptr())
+                                           self.head_k_dim, self.head_v_dim, self._summary_code, _lib.stream_ptr())
             _lib.check(rc, "va_gdn_compose")
         init = st["rw"][lin_idx].index_select(0, self._init_rows())    # read a/b, write a/b: [4, W]
         return self._scan(q, k, v, g, beta, st["segments"], state0, init, l2norm_eps, keep=st["keep"],

@@ -85,11 +85,17 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: the fields of
+    ``nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.*`` read
+    through NVML inside this process.  (Spawning nvidia-smi every 100 ms from the timed process
+    re-initialises NVML on every sample and holds driver locks that the step's own launches and
+    copies need: a host-bound step ran up to twice as long under it.)  Falls back to the
+    nvidia-smi command line when the NVML binding is missing."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    _nvml = None      # (module, {cuda index: handle}) once initialised; False when unavailable
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
@@ -97,19 +103,67 @@ class ClockSampler:
         self._stop = threading.Event()
         self._thread = None
 
+    @classmethod
+    def _handle(cls, gpu: int):
+        if cls._nvml is None:
+            try:
+                import pynvml
+                pynvml.nvmlInit()
+                cls._nvml = (pynvml, {})
+            except Exception:
+                cls._nvml = False
+        if not cls._nvml:
+            return None, None
+        nv, handles = cls._nvml
+        if gpu not in handles:
+            try:
+                uuid = getattr(torch.cuda.get_device_properties(gpu), "uuid", None)
+                handles[gpu] = (nv.nvmlDeviceGetHandleByUUID(f"GPU-{uuid}".encode()) if uuid is not None
+                                else nv.nvmlDeviceGetHandleByIndex(gpu))
+            except Exception:
+                try:
+                    handles[gpu] = nv.nvmlDeviceGetHandleByIndex(gpu)
+                except Exception:
+                    handles[gpu] = None
+        return nv, handles[gpu]
+
+    def _sample_nvml(self, nv, h) -> None:
+        sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        try:
+            watts = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+        except Exception:
+            watts = float("nan")
+        get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        r = int(get(h))
+        bits = [getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)]
+        self.samples.append([str(self.gpu), str(sm), str(mx), f"{watts:.1f}", hex(r)] +
+                            ["Active" if r & b else "Not Active" for b in bits])
+
+    def _sample_smi(self) -> None:
+        out = subprocess.run(
+            ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+             "-i", str(self.gpu)], capture_output=True, text=True, timeout=5).stdout.strip()
+        if out:
+            self.samples.append([c.strip() for c in out.split(",")])
+
     def _run(self):
+        nv, h = self._handle(self.gpu)
         while not self._stop.is_set():
             try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                     "-i", str(self.gpu)], capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([c.strip() for c in out.split(",")])
+                if h is not None:
+                    self._sample_nvml(nv, h)
+                else:
+                    self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.05 if h is not None else 0.2)
 
     def __enter__(self):
+        self._handle(self.gpu)     # NVML start-up happens before the timed region, not inside it
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
         return self
@@ -132,7 +186,7 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvml" if self._nvml else "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -333,12 +387,12 @@ def side_block_merge(device, iters, peaks, with_cpu):
     return res
 
 
-def _gdn_object(device):
+def _gdn_object(device, state_dtype=torch.float32):
     from async_llm_b200.view_gdn import SharedCacheGDN
 
     Hk, Hv, dk, dv = 16, 32, 128, 128
     ar = SharedCacheGDN(num_heads=Hv, head_k_dim=dk, head_v_dim=dv, conv_dim=2 * Hk * dk + Hv * dv,
-                        conv_kernel=4, device=device, num_k_heads=Hk)
+                        conv_kernel=4, device=device, num_k_heads=Hk, state_dtype=state_dtype)
     return ar, Hk, Hv, dk, dv
 
 
@@ -371,6 +425,16 @@ def side_gdn_step(device, iters, peaks, with_cpu):
            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
                         "frac": achieved / peaks["hbm"], "peak_kind": peaks["kind"], "traffic": None,
                         "algorithmic_bytes": algo}}
+    # the same step over bf16-stored summaries (the reference's optional state_dtype): half the bytes
+    ar16 = _gdn_object(device, torch.bfloat16)[0]
+    for b in [shared] + privs:
+        b.linear_affine[1] = tuple(t.to(torch.bfloat16) for t in b.linear_affine[0])
+    ar16.set_context(chains, privs)
+    ar16.prepare_decode(2, torch.bfloat16)
+    ms16 = time_graph(lambda: ar16.decode_step(1, q, k, v, g, beta), iters, device)
+    ar16.finish_decode(False)
+    res["bf16_summaries"] = {"ms": ms16, "tokens_per_s": W / (ms16 * 1e-3), "achieved": algo / 2 / ms16 / 1e6, "unit": "GB/s",
+                             "frac": algo / 2 / ms16 / 1e6 / peaks["hbm"], "algorithmic_bytes": algo // 2}
     if with_cpu:
         from oracle import gdn_oracle as go
 

@@ -209,6 +209,12 @@ int va_view_dense(const VaPool* pool, const VaDensePlan* plan, const void* q, in
  * per-token affine capture (shared_cache/gdn.py:213-269, kernel/gdn_prefill.py:53-131).
  * The new summaries go to FRESH slabs (write_a/write_b must not alias any input), so readers of
  * the previous summary are never disturbed (shared_cache/gdn_decode.py:112-121). */
+/* Storage type of block summaries (shared_cache/gdn.py:40-45, state_dtype): fp32, or bf16 storage
+ * with fp32 arithmetic -- values are widened when read and rounded once when a summary is stored
+ * (shared_cache/gdn.py:249-269, shared_cache/gdn_affine.py:113-122). */
+#define VA_SUMMARY_F32 0
+#define VA_SUMMARY_BF16 1
+
 typedef struct VaGdnStep {
   const void* q;            /* bf16 [W, num_k_heads, 128]                         */
   const void* k;            /* bf16 [W, num_k_heads, 128]                         */
@@ -231,6 +237,12 @@ typedef struct VaGdnStep {
   float l2_eps;
   float q_scale;
   int32_t* status;
+  /* elements between consecutive workers' rows of q / k / v (they may lie inside the wider
+   * [q | k | v] rows a layer's conv step wrote); 0 = dense */
+  int64_t q_row_stride;
+  int64_t k_row_stride;
+  int64_t v_row_stride;
+  int32_t summary_dtype;    /* VA_SUMMARY_*: storage type of every A_hat / B_hat named above */
 } VaGdnStep;
 
 int va_gdn_step(const VaGdnStep* args, va_stream_t stream);
@@ -241,7 +253,7 @@ int va_gdn_step(const VaGdnStep* args, va_stream_t stream);
  * GDNDecodeBuffers.compose shared_cache/gdn_decode.py:190-203. */
 int va_gdn_compose(const int64_t* chain_a, const int64_t* chain_b, float* state, int32_t num_workers,
                    int32_t depth, int32_t num_heads, int32_t head_k_dim, int32_t head_v_dim,
-                   va_stream_t stream);
+                   int32_t summary_dtype, va_stream_t stream);
 
 /* 5c. Prefill scan of a batch of requests (tokens request-major, request r owns rows
  * seg_off[r]:seg_off[r+1]): the gated delta rule from state0, the output rows, and the write
@@ -279,6 +291,7 @@ typedef struct VaGdnPrefill {
   void* scratch;
   int64_t scratch_bytes;
   int64_t num_tokens;       /* N (rows of q/k/v); needed with scratch              */
+  int32_t summary_dtype;    /* VA_SUMMARY_*: storage type of init_a/b and write_a/b */
 } VaGdnPrefill;
 
 /* SCAN: token by token in fp32 (exact restatement of the recurrence, state in registers).
@@ -418,12 +431,14 @@ int va_block_copy(const VaPool* pool, int32_t num_layers, int64_t layer_stride, 
 /* Replaces: the per-layer compose_gdn_affines calls of _finish_block_merge
  * (shared_cache/session.py:441-462; shared_cache/gdn_affine.py:104-127).  For every pair i:
  *   out_a[i] = a_first[i] a_second[i]          out_b[i] = b_first[i] a_second[i] + b_second[i]
- * per head, fp32.  The six arguments are device int64 arrays of device addresses of
- * [num_v_heads, 128, 128] fp32 tensors; outputs must not alias inputs. */
+ * per head, fp32 sums.  The six arguments are device int64 arrays of device addresses of
+ * [num_v_heads, 128, 128] tensors of the storage type summary_dtype (VA_SUMMARY_*; bf16 results are
+ * rounded once, after the fp32 add: shared_cache/gdn_affine.py:113-122); outputs must not alias
+ * inputs. */
 int va_gdn_compose_pairs(const int64_t* a_first, const int64_t* b_first, const int64_t* a_second,
                          const int64_t* b_second, const int64_t* out_a, const int64_t* out_b,
                          int32_t num_pairs, int32_t num_v_heads, int32_t head_k_dim, int32_t head_v_dim,
-                         va_stream_t stream);
+                         int32_t summary_dtype, va_stream_t stream);
 
 /* 9. Interleaved 3-axis mRoPE ----------------------------------------------------------------------
  * Replaces: SharedCacheAttention._rope_mrope shared_cache/attention.py:257-280 and, for the store
@@ -480,15 +495,20 @@ typedef struct VaGdnDecodePre {
   int32_t conv_dim;
   int32_t conv_kernel; /* 1..8 */
   int32_t num_v_heads;
+  int64_t a_row_stride; /* elements between workers' rows of a / b (columns of a wider      */
+  int64_t b_row_stride; /* projection output are read in place); 0 = num_v_heads            */
 } VaGdnDecodePre;
 
 int va_gdn_decode_pre(const VaGdnDecodePre* args, va_stream_t stream);
 
 /* Replaces _GatedRMSNorm.forward (models/qwen3_5_delta.py:248-263):
  *   out = bf16(weight * x * rsqrt(mean(x^2) + eps) * silu(gate)), fp32 inside.
- *   x, gate, out bf16 [rows, dim] contiguous; weight fp32 [dim]; dim a multiple of 32, <= 1024. */
+ *   x, out bf16 [rows, dim] contiguous; weight fp32 [dim]; dim a multiple of 32, <= 1024.
+ *   gate bf16: row r lies at gate + (r / rows_per_token) * gate_token_stride + (r % rows_per_token) * dim
+ *   (the z columns of a wider projection output are read in place); rows_per_token <= 0 = dense rows. */
 int va_gdn_gated_rmsnorm(const void* x, const void* gate, const float* weight, void* out, int64_t rows,
-                         int32_t dim, float eps, va_stream_t stream);
+                         int32_t dim, float eps, int32_t rows_per_token, int64_t gate_token_stride,
+                         va_stream_t stream);
 
 /* Replaces, per request of a GDN prefill (Qwen3_5GatedDeltaNet._forward_ar_prefill_one,
  * models/qwen3_5_delta.py:399-419), the transpose / concatenation with the prior conv tail,

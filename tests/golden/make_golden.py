@@ -11,6 +11,8 @@ Fixtures written (all inputs are seeded synthetic tensors):
                       by recorders (the trick of tests/core/test_attention_metadata.py:63-88)
   gdn_golden.npz      _recurrent_gated_delta_rule / _chunk_gated_delta_rule outputs
                       (minisgl/models/qwen3_5_delta.py) and gdn_affine update / compose results
+  gdn_bf16_golden.npz  SharedCacheGDN(state_dtype=bfloat16) eager capture / compose results
+                      (minisgl/shared_cache/gdn.py:127-269)
   gdn_layer_golden.npz  _decode_conv_silu, Qwen3_5GatedDeltaNet._gates and _GatedRMSNorm.forward outputs
                       (minisgl/models/qwen3_5_delta.py:232-263,296-299) on seeded bf16 inputs
   merge_golden.npz    KV pools, page lists, span overrides and recurrent summaries after
@@ -261,6 +263,65 @@ def make_gdn(ref):
     np.savez_compressed(os.path.join(HERE, "gdn_golden.npz"), **out)
 
 
+# ---- bf16 summary storage ---------------------------------------------------------------------
+BF16_CASE = dict(H=2, dk=128, dv=128, block_tokens={"a": 12, "b": 30, "c": 0, "w0": 3, "w1": 0, "w2": 0},
+                 chains=[["a", "c", "b", "w0"], ["b", "w1"], ["c"]], targets=["w0", "w1", "w2"], new_tokens=2)
+
+
+def gdn_bf16_inputs():
+    """Seeded tokens of the bf16-summary case: per block its tokens, then new_tokens per worker."""
+    c = BF16_CASE
+    g = torch.Generator().manual_seed(808)
+    H, dk, dv = c["H"], c["dk"], c["dv"]
+
+    def tokens(T):
+        k = torch.randn(T, H, dk, generator=g).to(torch.bfloat16)
+        v = torch.randn(T, H, dv, generator=g).to(torch.bfloat16)
+        alpha = torch.sigmoid(torch.randn(T, H, generator=g) + 2.0)
+        beta = torch.sigmoid(torch.randn(T, H, generator=g))
+        return k, v, alpha, beta
+
+    data = {name: tokens(T) for name, T in c["block_tokens"].items()}
+    data["new"] = tokens(len(c["targets"]) * c["new_tokens"])
+    return data
+
+
+def make_gdn_bf16(ref):
+    """Reference SharedCacheGDN(state_dtype=bfloat16), eager path on CPU: summaries captured block by
+    block, the chains composed, two more tokens captured into the write blocks."""
+    from minisgl.shared_cache.gdn import SharedCacheGDN
+    from minisgl.shared_cache.shared_block import CacheBlock
+
+    c = BF16_CASE
+    H, dk, dv = c["H"], c["dk"], c["dv"]
+    data = gdn_bf16_inputs()
+    cpu = torch.device("cpu")
+    ar = SharedCacheGDN(num_heads=H, head_k_dim=dk, head_v_dim=dv, conv_dim=2 * H * dk + H * dv, conv_kernel=4,
+                        device=cpu, state_dtype=torch.bfloat16)
+    blocks = {name: CacheBlock(cpu, 16) for name in c["block_tokens"]}
+    out = {}
+    for name, T in c["block_tokens"].items():
+        if T == 0:
+            continue
+        k, v, alpha, beta = data[name]
+        ar.set_context([[blocks[name]]], [blocks[name]])
+        ar.capture_token_affines(0, k[None], v[None], alpha[None], beta[None])
+        A, Bm = blocks[name].linear_affine[0]
+        assert A.dtype == torch.bfloat16
+        out[f"{name}_A"], out[f"{name}_B"] = bf16_bits(A), bf16_bits(Bm)
+    chains = [[blocks[n] for n in ch] for ch in c["chains"]]
+    targets = [blocks[n] for n in c["targets"]]
+    ar.set_context(chains, targets)
+    out["S0"] = ar.compose_initial_recurrent_state(0, torch.float32).numpy()
+    k, v, alpha, beta = data["new"]
+    W, n = len(targets), c["new_tokens"]
+    ar.capture_token_affines(0, k.view(W, n, H, dk), v.view(W, n, H, dv), alpha.view(W, n, H), beta.view(W, n, H))
+    for w, t in enumerate(targets):
+        A, Bm = t.linear_affine[0]
+        out[f"new{w}_A"], out[f"new{w}_B"] = bf16_bits(A), bf16_bits(Bm)
+    np.savez_compressed(os.path.join(HERE, "gdn_bf16_golden.npz"), **out)
+
+
 # ---- block merge / append -------------------------------------------------------------------
 MERGE_SHAPE = dict(layers=2, pages=24, P=4, Hkv=2, D=64, max_pos=256, base=1e4, H=2, dk=8, dv=8)
 
@@ -402,6 +463,7 @@ if __name__ == "__main__":
     sys.path.insert(0, os.path.join(ref, "python"))
     make_rope(ref)
     make_gdn(ref)
+    make_gdn_bf16(ref)
     make_merge(ref)
     make_gdn_layer(ref)
     make_plans(ref)
