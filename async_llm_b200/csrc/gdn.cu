@@ -53,18 +53,36 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
-// summary rows a warp has outstanding: fp32 rows (512 bytes) 4 (4: 4.95 TB/s, 8: 4.71, 1: 3.83 on
-// config 4b); bf16 rows are half as long, so twice as many keep the same bytes in flight
+// Row-group mapping of the step kernel: eight lanes share a summary row (lane l of the eight owns
+// columns i * 32 + 4 l .. + 3, i = 0..3: every 16-byte piece a lane loads sits in a 128-byte run of
+// its row), so a warp works on four consecutive rows at once and a dot product needs three shuffle
+// steps for four rows instead of five per row.  (With one row per warp the two 5-step reductions
+// per row -- 20 shuffles, a quarter-rate instruction -- cost more than the row's memory time: bf16
+// rows, half the bytes, ran no faster than fp32 rows.)
+// Row groups a warp has in flight: 2 x 2 KB of fp32 rows, 4 x 1 KB of bf16 rows.
 template <bool kBf16>
-constexpr int kRowsInFlight = kBf16 ? 8 : 4;
+constexpr int kGroupsInFlight = kBf16 ? 4 : 2;
+
+__device__ __forceinline__ float dot4(float4 a, float4 b, float acc) {
+  acc = fmaf(a.x, b.x, acc);
+  acc = fmaf(a.y, b.y, acc);
+  acc = fmaf(a.z, b.z, acc);
+  return fmaf(a.w, b.w, acc);
+}
+// sum over the eight lanes that share a row
+__device__ __forceinline__ float row_sum(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  return x;
+}
 
 // grid (Hv, W), 256 threads.  Vectors live in shared memory as fp32.
-// (5 CTAs per SM, 48 registers: +8 % over the 4 CTAs that the unconstrained 60 registers allow; 6 and 8
-// CTAs spill more than they gain)
 template <bool kBf16>
-__global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant__ StepParams p) {
+__global__ void __launch_bounds__(256, 3) gdn_step_kernel(const __grid_constant__ StepParams p) {
   using IO = SumIO<kBf16>;
-  constexpr int RF = kRowsInFlight<kBf16>;
+  constexpr int GF = kGroupsInFlight<kBf16>;
+  constexpr int kPassRows = 8 * GF * 4;      // rows the CTA's eight warps cover per pass
   __shared__ __align__(16) float kn[kD];   // l2-normalised key
   __shared__ __align__(16) float qn[kD];   // l2-normalised, scaled query
   __shared__ __align__(16) float vv[kD];
@@ -78,6 +96,8 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  const int r4 = lane >> 3;   // row of the warp's group
+  const int l8 = lane & 7;    // position among the row's eight lanes
   const int hk = h / (p.num_v_heads / p.num_k_heads);
 
   // ---- load and normalise the token's vectors
@@ -111,62 +131,82 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
   const float bt = p.beta[static_cast<int64_t>(w) * p.num_v_heads + h];
   const float alpha = __expf(gate);
   const float ab = alpha * bt;  // same association as alpha_b * beta_b in update_affine_summary
-  const float4 k4 = *reinterpret_cast<const float4*>(kn + lane * 4);
-  const float4 q4 = *reinterpret_cast<const float4*>(qn + lane * 4);
+  // this lane's columns of the key (registers); the query's are read from shared memory when needed
+  float4 kc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) kc[i] = *reinterpret_cast<const float4*>(kn + i * 32 + l8 * 4);
 
-  // ---- phase 1: the write block's summary, one row per warp pass: dot with k and q, rank-1
-  //      update, write the fresh row.  rows 0..127 are A_hat, 128..255 are B_hat.
+  // ---- phase 1: the write block's summary: dot every row with k and q, rank-1 update, write the
+  //      fresh row.  rows 0..127 are A_hat, 128..255 are B_hat (a group of four rows lies in one).
   const void* ra = reinterpret_cast<const void*>(p.read_a[w]);
   const void* rb = reinterpret_cast<const void*>(p.read_b[w]);
   void* wa = reinterpret_cast<void*>(p.write_a[w]);
   void* wb = reinterpret_cast<void*>(p.write_b[w]);
   const int64_t head_off = static_cast<int64_t>(h) * kD * kD;
-  // A warp takes RF consecutive rows per pass and fetches all of them before it reduces the first:
-  // with one row in flight per warp the SM had too few bytes outstanding to cover the HBM latency.
-  for (int r0 = warp * RF; r0 < 2 * kD; r0 += 8 * RF) {
-    typename IO::Raw xr[RF];
+  // A warp fetches all the groups of a pass before it reduces the first: with little in flight per
+  // warp the SM had too few bytes outstanding to cover the HBM latency.
+  for (int r0 = warp * (GF * 4); r0 < 2 * kD; r0 += kPassRows) {
+    typename IO::Raw xr[GF][4];
 #pragma unroll
-    for (int u = 0; u < RF; ++u) {
-      const int r = r0 + u;
+    for (int u = 0; u < GF; ++u) {
+      const int r = r0 + u * 4 + r4;
       const bool is_b = r >= kD;
       const int row = is_b ? r - kD : r;
       const void* src = is_b ? rb : ra;
       // read once (and rewritten below): streaming loads and stores keep the chain blocks, which
       // every worker re-reads, in L2
-      if (src != nullptr) xr[u] = IO::ld_stream(src, head_off + static_cast<int64_t>(row) * kD + lane * 4);
+      if (src != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          xr[u][i] = IO::ld_stream(src, head_off + static_cast<int64_t>(row) * kD + i * 32 + l8 * 4);
+      }
     }
 #pragma unroll
-    for (int u = 0; u < RF; ++u) {
-      const int r = r0 + u;
+    for (int u = 0; u < GF; ++u) {
+      const int r = r0 + u * 4 + r4;
       const bool is_b = r >= kD;
       const int row = is_b ? r - kD : r;
-      float4 x;
+      float4 x[4];
       if ((is_b ? rb : ra) != nullptr) {
-        x = IO::widen(xr[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = IO::widen(xr[u][i]);
       } else {
         // no summary yet: A_hat = I, B_hat = 0
-        x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!is_b && (row >> 2) == lane) reinterpret_cast<float*>(&x)[row & 3] = 1.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c0 = is_b ? -8 : i * 32 + l8 * 4;   // first column of the piece (none matches for B_hat)
+          x[i] = make_float4(row == c0 ? 1.f : 0.f, row == c0 + 1 ? 1.f : 0.f, row == c0 + 2 ? 1.f : 0.f,
+                             row == c0 + 3 ? 1.f : 0.f);
+        }
       }
-      const float dk_ = warp_sum(x.x * k4.x + x.y * k4.y + x.z * k4.z + x.w * k4.w);
-      const float dq_ = warp_sum(x.x * q4.x + x.y * q4.y + x.z * q4.z + x.w * q4.w);
+      float dk_ = 0.f, dq_ = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        dk_ = dot4(x[i], kc[i], dk_);
+        dq_ = dot4(x[i], *reinterpret_cast<const float4*>(qn + i * 32 + l8 * 4), dq_);
+      }
+      dk_ = row_sum(dk_);
+      dq_ = row_sum(dq_);
       // A' = alpha A - (alpha beta (A k)) k^T ;  B' = alpha B - (alpha beta (B k)) k^T + (beta v) k^T
       const float t1 = ab * dk_;
-      float4 y;
-      y.x = __fsub_rn(__fmul_rn(alpha, x.x), __fmul_rn(t1, k4.x));
-      y.y = __fsub_rn(__fmul_rn(alpha, x.y), __fmul_rn(t1, k4.y));
-      y.z = __fsub_rn(__fmul_rn(alpha, x.z), __fmul_rn(t1, k4.z));
-      y.w = __fsub_rn(__fmul_rn(alpha, x.w), __fmul_rn(t1, k4.w));
-      if (is_b) {
-        const float t2 = bt * vv[row];
-        y.x = __fadd_rn(y.x, __fmul_rn(t2, k4.x));
-        y.y = __fadd_rn(y.y, __fmul_rn(t2, k4.y));
-        y.z = __fadd_rn(y.z, __fmul_rn(t2, k4.z));
-        y.w = __fadd_rn(y.w, __fmul_rn(t2, k4.w));
-      }
+      const float t2 = is_b ? bt * vv[row] : 0.f;
       void* dst = is_b ? wb : wa;
-      if (dst != nullptr) IO::st_stream(dst, head_off + static_cast<int64_t>(row) * kD + lane * 4, y);
-      if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 y;
+        y.x = __fsub_rn(__fmul_rn(alpha, x[i].x), __fmul_rn(t1, kc[i].x));
+        y.y = __fsub_rn(__fmul_rn(alpha, x[i].y), __fmul_rn(t1, kc[i].y));
+        y.z = __fsub_rn(__fmul_rn(alpha, x[i].z), __fmul_rn(t1, kc[i].z));
+        y.w = __fsub_rn(__fmul_rn(alpha, x[i].w), __fmul_rn(t1, kc[i].w));
+        if (is_b) {
+          y.x = __fadd_rn(y.x, __fmul_rn(t2, kc[i].x));
+          y.y = __fadd_rn(y.y, __fmul_rn(t2, kc[i].y));
+          y.z = __fadd_rn(y.z, __fmul_rn(t2, kc[i].z));
+          y.w = __fadd_rn(y.w, __fmul_rn(t2, kc[i].w));
+        }
+        if (dst != nullptr) IO::st_stream(dst, head_off + static_cast<int64_t>(row) * kD + i * 32 + l8 * 4, y);
+      }
+      if (l8 == 0) {
         if (is_b) {
           // contribution of the write block if it closes the chain (used in phase 2)
           uk[1][row] = dk_;  // scratch: B_w k
@@ -208,36 +248,44 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
       fresh = false;
       continue;
     }
-    // current vectors as registers (4 values per lane)
-    float4 ck, cq;
-    if (fresh) {
-      ck = k4;
-      cq = q4;
-    } else {
-      ck = *reinterpret_cast<const float4*>(uk[cur] + lane * 4);
-      cq = *reinterpret_cast<const float4*>(uq[cur] + lane * 4);
+    // current vectors: this lane's columns, as registers
+    const float* vk = fresh ? kn : uk[cur];
+    const float* vq = fresh ? qn : uq[cur];
+    float4 ck[4], cq[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      ck[i] = *reinterpret_cast<const float4*>(vk + i * 32 + l8 * 4);
+      cq[i] = *reinterpret_cast<const float4*>(vq + i * 32 + l8 * 4);
     }
     const int nxt = fresh ? 0 : cur ^ 1;
     __syncthreads();  // everyone has read uk[cur] before uk[nxt] (== scratch) is overwritten
     const int n_rows = earlier ? 2 * kD : kD;
-    for (int r0 = warp * RF; r0 < n_rows; r0 += 8 * RF) {   // as in phase 1
-      typename IO::Raw xr[RF];
+    for (int r0 = warp * (GF * 4); r0 < n_rows; r0 += kPassRows) {   // as in phase 1
+      typename IO::Raw xr[GF][4];
 #pragma unroll
-      for (int u = 0; u < RF; ++u) {
-        const int r = r0 + u;
+      for (int u = 0; u < GF; ++u) {
+        const int r = r0 + u * 4 + r4;
         const bool is_a = r >= kD;
         const int row = is_a ? r - kD : r;
-        xr[u] = IO::ld(is_a ? aj : bj, head_off + static_cast<int64_t>(row) * kD + lane * 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          xr[u][i] = IO::ld(is_a ? aj : bj, head_off + static_cast<int64_t>(row) * kD + i * 32 + l8 * 4);
       }
 #pragma unroll
-      for (int u = 0; u < RF; ++u) {
-        const int r = r0 + u;
+      for (int u = 0; u < GF; ++u) {
+        const int r = r0 + u * 4 + r4;
         const bool is_a = r >= kD;
         const int row = is_a ? r - kD : r;
-        const float4 x = IO::widen(xr[u]);
-        const float dk_ = warp_sum(x.x * ck.x + x.y * ck.y + x.z * ck.z + x.w * ck.w);
-        const float dq_ = warp_sum(x.x * cq.x + x.y * cq.y + x.z * cq.z + x.w * cq.w);
-        if (lane == 0) {
+        float dk_ = 0.f, dq_ = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 x = IO::widen(xr[u][i]);
+          dk_ = dot4(x, ck[i], dk_);
+          dq_ = dot4(x, cq[i], dq_);
+        }
+        dk_ = row_sum(dk_);
+        dq_ = row_sum(dq_);
+        if (l8 == 0) {
           if (is_a) {
             uk[nxt][row] = dk_;
             uq[nxt][row] = dq_;
@@ -256,6 +304,8 @@ __global__ void __launch_bounds__(256, 5) gdn_step_kernel(const __grid_constant_
   // ---- phase 3: one recurrent token on X0 without forming it.
   //      kv = alpha X0 k ; delta = (v - kv) beta ; o = alpha X0 q + delta (k.q)
   {
+    const float4 k4 = *reinterpret_cast<const float4*>(kn + lane * 4);
+    const float4 q4 = *reinterpret_cast<const float4*>(qn + lane * 4);
     const float kq = warp_sum(k4.x * q4.x + k4.y * q4.y + k4.z * q4.z + k4.w * q4.w);
     if (tid < kD) {
       const float kv = alpha * yk[tid];

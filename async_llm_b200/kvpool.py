@@ -14,8 +14,9 @@ from __future__ import annotations
 
 import ctypes as C
 from abc import ABC, abstractmethod
-from typing import Optional
+from typing import List, Optional
 
+import numpy as np
 import torch
 
 from . import _lib
@@ -191,17 +192,22 @@ def store_rows(kv_cache, k, v, out_loc, layer_id, positions, cos_sin, rotary_dim
 
 
 class PageAllocator:
-    """Free list of page-start slots ``[0, P, 2P, ...]`` kept as a device int32 tensor.
+    """Free list of page-start slots ``[0, P, 2P, ...]`` kept as a device int32 tensor
+    (minisgl/kvcache/page_allocator.py:6-62), with a host copy of the same list beside it.
 
     ``alloc_pages(n)`` takes the first ``n`` entries, ``free_pages`` appends; exhaustion raises
-    ``RuntimeError`` before anything is handed out.
+    ``RuntimeError`` before anything is handed out.  ``alloc_page_list(n)`` is the same allocation
+    answered from the host copy: the write planner needs the page numbers as Python ints, and
+    reading them back from the device tensor waits for everything queued on the stream (a decode
+    step that crossed a page boundary lost the overlap of its planning with the previous step).
     """
 
     def __init__(self, num_pages: int, page_size: int, device: torch.device) -> None:
         self.num_pages = num_pages
         self.page_size = page_size
         self.device = device
-        self._free = torch.arange(num_pages, dtype=torch.int32, device=device) * page_size
+        self._free_host = np.arange(num_pages, dtype=np.int32) * page_size
+        self._free = torch.from_numpy(self._free_host.copy()).to(device)
 
     @property
     def num_free_pages(self) -> int:
@@ -217,17 +223,34 @@ class PageAllocator:
         lane = torch.arange(self.page_size, dtype=page_starts.dtype, device=page_starts.device)
         return (page_starts.unsqueeze(1) + lane.unsqueeze(0)).reshape(-1)
 
-    def alloc_pages(self, num_pages: int) -> torch.Tensor:
+    def _take(self, num_pages: int):
         have = self.num_free_pages
         if num_pages > have:
             raise RuntimeError(
                 f"PageAllocator out of pages: requested {num_pages}, only {have} free"
             )
-        taken, self._free = self._free[:num_pages].clone(), self._free[num_pages:]
-        return taken
+        taken, self._free = self._free[:num_pages], self._free[num_pages:]
+        host, self._free_host = self._free_host[:num_pages], self._free_host[num_pages:]
+        return taken, host
 
-    def free_pages(self, page_starts: torch.Tensor) -> None:
-        if page_starts.numel() == 0:
-            return
-        back = page_starts.to(device=self._free.device, dtype=self._free.dtype)
+    def alloc_pages(self, num_pages: int) -> torch.Tensor:
+        return self._take(num_pages)[0].clone()
+
+    def alloc_page_list(self, num_pages: int) -> List[int]:
+        """``alloc_pages(num_pages)`` as a list of ints, without touching the device."""
+        return self._take(num_pages)[1].tolist()
+
+    def free_pages(self, page_starts) -> None:
+        """Give pages back: a tensor (device or host) or a sequence of page-start slots."""
+        if isinstance(page_starts, torch.Tensor):
+            if page_starts.numel() == 0:
+                return
+            host = page_starts.detach().to("cpu", torch.int32).numpy()
+            back = page_starts.to(device=self._free.device, dtype=self._free.dtype)
+        else:
+            host = np.asarray(list(page_starts), dtype=np.int32)
+            if host.size == 0:
+                return
+            back = torch.from_numpy(host).to(self._free.device)
         self._free = torch.cat((self._free, back))
+        self._free_host = np.concatenate((self._free_host, host))

@@ -23,7 +23,9 @@ def plan_decode_writes(group: WorkerGroup, page_allocator, page_size: int, devic
     Returns ``(new_page_for_block, new_token_slots, write_pos)``: ``id(block) ->`` page-start slot
     of a freshly borrowed page (or None), the ``[W]`` int32 destination slots, and the
     block-relative RoPE position of each write (the block's mRoPE span).  All blocks whose last
-    page is full share ONE ``alloc_pages`` call and one device-to-host readback.
+    page is full share ONE allocation; an allocator that keeps a host copy of its free list
+    (``alloc_page_list``) answers it without a device-to-host readback, which would wait for
+    everything queued on the stream.
     """
     pending: Dict[int, Optional[int]] = {}
     full: List[CacheBlock] = []
@@ -34,7 +36,8 @@ def plan_decode_writes(group: WorkerGroup, page_allocator, page_size: int, devic
         if not target.has_capacity:
             full.append(target)
     if full:
-        fresh = page_allocator.alloc_pages(len(full)).cpu().tolist()
+        take = getattr(page_allocator, "alloc_page_list", None)
+        fresh = take(len(full)) if take is not None else page_allocator.alloc_pages(len(full)).cpu().tolist()
         for target, start in zip(full, fresh):
             pending[id(target)] = start
     slots: List[int] = []

@@ -393,7 +393,8 @@ class SharedCacheGDN:
                 if not hasattr(target, "_gdn_revision"):
                     continue
                 if full_a:
-                    target._gdn_ptr_cache = (target._gdn_revision, self.device, new_ptrs[w], [slab_a, slab_b])
+                    target._gdn_ptr_cache = (target._gdn_revision, (self.device, self.state_dtype), new_ptrs[w],
+                                             [slab_a, slab_b])
                 if len(conv_layers) == layers and full_c:
                     target._gdn_conv_cache = (target._gdn_revision, self.device,
                                               np.ascontiguousarray(st["host"][ROW_CONV_WRITE, :, w, 0]), [conv_slab])

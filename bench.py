@@ -598,6 +598,9 @@ def run_hybrid(device, steps: int, warmup: int, peaks, rank: int, world: int, pe
         for d in descs:
             d.output_block.num_tokens += 1
 
+    # (the first steps after the capture also grow the caching allocator's pool of summary slabs --
+    # every step hands each write block fresh A_hat / B_hat tensors, 3.2 GB at 32 requests -- and a
+    # cudaMalloc synchronises the device: the warm-up has to reach the steady state of that pool)
     for k in range(warmup):
         step(k)
     barrier()
@@ -779,7 +782,7 @@ def main() -> None:
         from async_llm_b200.sharding import BlockReplicator
 
         alloc = PageAllocator(0, args.page_size, device)
-        alloc._free = torch.tensor(case.free_pages[-n_shared:], dtype=torch.int32, device=device)
+        alloc.free_pages(torch.tensor(case.free_pages[-n_shared:], dtype=torch.int32))
         case.free_pages = case.free_pages[:-n_shared]
         rep = BlockReplicator(dv.pool, alloc)
         shared = case.blocks["shared"] if rank == 0 else CacheBlock(torch.device("cpu"), args.page_size)
@@ -1038,7 +1041,7 @@ def main() -> None:
     if not args.no_side and not args.no_hybrid and default_workload:
         # the full-model workload runs on every rank (requests sharded over the GPUs)
         try:
-            sides["hybrid"] = run_hybrid(device, 10, 3, peaks, rank, world)
+            sides["hybrid"] = run_hybrid(device, 10, 8, peaks, rank, world)
         except Exception as exc:   # noqa: BLE001
             sides["hybrid"] = {"error": f"{type(exc).__name__}: {exc}"}
             if world > 1:

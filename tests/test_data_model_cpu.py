@@ -108,6 +108,23 @@ def test_page_allocator_hands_out_and_takes_back():
     assert alloc.alloc_pages(0).numel() == 0
 
 
+def test_page_allocator_host_list_tracks_the_device_list():
+    # the host copy answers the write planner without a device readback; it must hand out the same
+    # pages in the same order as alloc_pages and see every page that comes back
+    alloc = PageAllocator(num_pages=6, page_size=4, device=CPU)
+    assert alloc.alloc_page_list(2) == [0, 4]
+    assert alloc.alloc_pages(1).tolist() == [8]
+    assert alloc.free_page_starts.tolist() == [12, 16, 20] and alloc.num_free_pages == 3
+    alloc.free_pages(torch.tensor([4], dtype=torch.int32))
+    alloc.free_pages([0])
+    alloc.free_pages([])
+    assert alloc.free_page_starts.tolist() == [12, 16, 20, 4, 0]
+    assert alloc.alloc_page_list(4) == [12, 16, 20, 4]
+    with pytest.raises(RuntimeError):
+        alloc.alloc_page_list(2)
+    assert alloc.alloc_page_list(1) == [0] and alloc.num_free_pages == 0
+
+
 def test_write_planning_borrows_one_page_per_full_block():
     P = 4
     alloc = PageAllocator(num_pages=8, page_size=P, device=CPU)
