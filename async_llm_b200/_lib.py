@@ -173,6 +173,7 @@ class VaAttnQkNorm(C.Structure):
 
 
 SUMMARY_F32, SUMMARY_BF16 = 0, 1   # VA_SUMMARY_*
+VA_PHASE_GROUPS_FORKED = 8
 
 
 def summary_code(dtype) -> int:
@@ -199,6 +200,8 @@ SIGNATURES = {
     "va_view_decode": (C.c_int, [C.POINTER(VaPool), C.POINTER(VaDecodePlan), C.c_void_p, C.c_int64,
                                  C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p]),
+    "va_view_decode_fork_groups": (C.c_int, [C.POINTER(VaPool), C.POINTER(VaDecodePlan), C.c_void_p, C.c_int64,
+                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "va_view_dense": (C.c_int, [C.POINTER(VaPool), C.POINTER(VaDensePlan), C.c_void_p, C.c_int64,
                                 C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                 C.c_void_p]),

@@ -32,6 +32,9 @@ struct StoreParams {
 
 // grid.x = token, threads stride over the row's heads*head_dim elements (pairs of bf16).
 __global__ void __launch_bounds__(256) store_kv_kernel(const __grid_constant__ StoreParams p) {
+  // a kernel launched behind this one as a programmatic dependent (the streaming pass of a decode
+  // step) may become resident now; it waits for this grid to complete before it reads the pools
+  pdl_launch_dependents();
   const int tok = blockIdx.x;
   if (tok >= p.n) return;
   const int slot = p.out_loc[tok];

@@ -253,6 +253,9 @@ __global__ void __launch_bounds__(StreamCfg<D>::kWarps * 64, 1)
 
   if (producer) {
     // =================================================================== producer
+    // (when this grid was launched as a programmatic dependent of the kernel that stores the step's
+    // new keys, its prologue ran beside that kernel; the pools may only be read from here on)
+    pdl_wait();
     // streamed keys and values are read once: they should not push a shared block that the dense
     // tiles re-read out of L2
     const uint64_t stream_policy = l2_policy_evict_first();
@@ -616,11 +619,21 @@ int launch_decode(const DecodeParams& p, int sm_count, cudaStream_t stream) {
     if (e != cudaSuccess) return va_host::note_cuda_error(e);
   }
   if ((p.phase_mask & VA_PHASE_SKIP_STREAM) == 0 && p.num_items > 0) {
-    // (a plain launch: letting this kernel start under the store kernel before it changed where its
-    // CTAs land relative to the dense tiles' and cost 4 us per step)
-    if (bulk) view_decode_stream_kernel<D, true><<<blocks, Cfg::kWarps * 64, Sm::kTotalBytes, stream>>>(p);
-    else view_decode_stream_kernel<D, false><<<blocks, Cfg::kWarps * 64, Sm::kTotalBytes, stream>>>(p);
-    cudaError_t e = cudaGetLastError();
+    // A plain launch, unless the dense tiles were forked before the store kernel
+    // (VA_PHASE_GROUPS_FORKED): they then hold their SMs already and this grid may become resident
+    // under the store kernel.  (Letting it start early while the dense tiles still waited for the
+    // store changed where its CTAs land relative to theirs and cost 4 us per step.)
+    cudaError_t e;
+    if ((p.phase_mask & VA_PHASE_GROUPS_FORKED) != 0) {
+      e = bulk ? va_host::launch_dependent(view_decode_stream_kernel<D, true>, dim3(blocks), dim3(Cfg::kWarps * 64),
+                                           Sm::kTotalBytes, stream, p)
+               : va_host::launch_dependent(view_decode_stream_kernel<D, false>, dim3(blocks), dim3(Cfg::kWarps * 64),
+                                           Sm::kTotalBytes, stream, p);
+    } else {
+      if (bulk) view_decode_stream_kernel<D, true><<<blocks, Cfg::kWarps * 64, Sm::kTotalBytes, stream>>>(p);
+      else view_decode_stream_kernel<D, false><<<blocks, Cfg::kWarps * 64, Sm::kTotalBytes, stream>>>(p);
+      e = cudaGetLastError();
+    }
     if (e != cudaSuccess) return va_host::note_cuda_error(e);
   }
   if ((p.phase_mask & VA_PHASE_SKIP_MERGE) == 0) {
@@ -758,7 +771,12 @@ extern "C" int va_view_decode(const VaPool* pool, const VaDecodePlan* plan, cons
   SideStream* side = nullptr;
   const bool with_groups = plan->groups != nullptr && plan->groups->num_tiles > 0 &&
                            (plan->phase_mask & VA_PHASE_SKIP_GROUPS) == 0;
-  if (with_groups) {
+  const bool forked = with_groups && (plan->phase_mask & VA_PHASE_GROUPS_FORKED) != 0;
+  if (forked) {
+    // va_view_decode_fork_groups launched the tiles earlier on this stream: only the join is left
+    rc = side_stream(&side);
+    if (rc != VA_OK) return rc;
+  } else if (with_groups) {
     rc = side_stream(&side);
     if (rc != VA_OK) return rc;
     cudaError_t e = cudaEventRecord(side->fork, s);
@@ -772,6 +790,7 @@ extern "C" int va_view_decode(const VaPool* pool, const VaDecodePlan* plan, cons
   }
   const int merge_mask = p.phase_mask;
   p.phase_mask |= VA_PHASE_SKIP_MERGE;
+  if (!forked) p.phase_mask &= ~VA_PHASE_GROUPS_FORKED;
   if (pool->head_dim == 256) rc = launch_decode<256>(p, 0, s);
   else if (pool->head_dim == 128) rc = launch_decode<128>(p, 0, s);
   else rc = VA_ERR_UNSUPPORTED;
@@ -786,6 +805,32 @@ extern "C" int va_view_decode(const VaPool* pool, const VaDecodePlan* plan, cons
     else rc = launch_decode<128>(p, 0, s);
   }
   return rc;
+}
+
+// The dense tiles of a step, launched ahead of the rest: forked from `stream` where it stands (before
+// the kernel that stores the step's new keys), joined by the va_view_decode call that follows on the
+// same stream with VA_PHASE_GROUPS_FORKED set.
+extern "C" int va_view_decode_fork_groups(const VaPool* pool, const VaDecodePlan* plan, const void* q,
+                                          int64_t q_row_stride, float* partial_o, float* partial_ml,
+                                          int32_t* status, va_stream_t stream) {
+  if (pool == nullptr || plan == nullptr || plan->groups == nullptr || q == nullptr || partial_o == nullptr ||
+      partial_ml == nullptr)
+    return VA_ERR_BAD_ARG;
+  if (plan->groups->num_tiles <= 0) return VA_OK;
+  if (plan->groups->num_partials > plan->num_partials) return VA_ERR_CAPACITY;
+  SideStream* side = nullptr;
+  int rc = side_stream(&side);
+  if (rc != VA_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaEventRecord(side->fork, s);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(side->stream, side->fork, 0);
+  if (e != cudaSuccess) return va_host::note_cuda_error(e);
+  // (mode-1 tiles write partials only: no output rows are needed here)
+  rc = va_view_dense(pool, plan->groups, q, q_row_stride, nullptr, 0, partial_o, partial_ml, status, side->stream);
+  if (rc != VA_OK) return rc;
+  e = cudaEventRecord(side->join, side->stream);
+  if (e != cudaSuccess) return va_host::note_cuda_error(e);
+  return VA_OK;
 }
 
 // ------------------------------------------------------------------------------------------------

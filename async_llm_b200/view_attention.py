@@ -216,12 +216,16 @@ class DensePlan:
     host: Dict[str, np.ndarray]
 
 
+# VIEWATTN_FORK_DENSE=0 keeps the dense tiles of a decode step behind the store kernel (comparisons)
+FORK_DENSE_EARLY = os.environ.get("VIEWATTN_FORK_DENSE", "1") != "0"
+
+
 class _ViewTopology:
     """Flattened structure of a worker group's views: valid while the same blocks sit in the same
     views with the same write blocks, whatever their lengths and page lists do meanwhile."""
 
     __slots__ = ("key", "blocks", "index", "targets", "view_blk", "view_start", "aux_w", "aux_w_np",
-                 "written_flag", "subs")
+                 "written_flag", "subs", "written_max_readers")
 
     def __init__(self, key, workers, written):
         self.key = key
@@ -250,6 +254,10 @@ class _ViewTopology:
         self.aux_w = aux_w
         self.aux_w_np = np.asarray(aux_w, np.int32)
         self.written_flag = np.fromiter((id(b) in written for b in blocks), np.int32, len(blocks))
+        # how many views read the most widely read block that is written this step: the dense tiles of
+        # a step only depend on the step's new keys if such a block is read widely enough to be tiled
+        readers = np.bincount(self.view_blk, minlength=len(blocks)) if len(view_blk) else np.zeros(len(blocks), np.int64)
+        self.written_max_readers = int((readers * self.written_flag).max()) if len(blocks) else 0
         self.subs = np.empty((5, max(len(view_blk) + len(aux_w), 1)), np.int32)   # filled by the planner
 
 
@@ -703,6 +711,11 @@ class SharedCacheAttention:
         meta._table_recipe = (sub_out[4, :n_main], sub_out[3, :n_main], run_len, plan.host["page_indices"], aux_kv, P)
         meta.plan = plan
         meta.graph_buffers = graph_buffers
+        # the dense tiles may be launched before the step's keys are stored when no block they could
+        # cover is written in the step; a plan that is re-made behind a captured graph keeps the
+        # conservative order, because the launch order is part of the capture
+        meta.fork_dense_early = (graph_buffers is None and plan.groups is not None
+                                 and topo.written_max_readers < self.GROUP_MIN_READERS)
         if graph_buffers is not None:
             meta.num_workers = graph_buffers.workers
         return meta
@@ -837,13 +850,31 @@ class SharedCacheAttention:
             pos = batch.positions if mrope_positions is None else mrope_positions
             meta._pos32 = (pos if pos.dtype == torch.int32 else pos.to(torch.int32)).contiguous()
         status = self.status()
+        forked = False
+        if meta.phase != "prefill_batch" and getattr(meta, "fork_dense_early", False) and FORK_DENSE_EARLY:
+            # the tiles of the widely read blocks start now, beside the store kernel
+            q = self._decode_queries(q, meta)
+            plan = meta.plan
+            self._reserve_partials(plan.num_partials)
+            pool = pool_struct(self.kv_cache, layer_id, self.num_qo_heads, self._cos_sin, self.rotary_dim)
+            rc = _lib.lib().va_view_decode_fork_groups(
+                C.byref(pool), C.byref(plan.struct), q.data_ptr(), q.stride(0), self._partial_o.data_ptr(),
+                self._partial_ml.data_ptr(), status.data_ptr(), _lib.stream_ptr())
+            _lib.check(rc, "va_view_decode_fork_groups")
+            forked = True
         store_rows(self.kv_cache, k, v, batch.out_loc, layer_id, meta._pos32, self._cos_sin,
                    self.rotary_dim, status=status,
                    mrope_lims=self._mrope_lims if self.mrope_section is not None else None)
-        return self._attend(q, meta, layer_id)
+        return self._attend(q, meta, layer_id, forked=forked)
 
-    def _attend(self, q: torch.Tensor, meta: SharedCacheAttnMetadata, layer_id: int) -> torch.Tensor:
-        """The attention of a planned step over keys that are already in the pool."""
+    @staticmethod
+    def _decode_queries(q: torch.Tensor, meta: SharedCacheAttnMetadata) -> torch.Tensor:
+        q2 = q.reshape(meta.num_workers, -1)
+        return q2 if q2.stride(1) == 1 else q2.contiguous()
+
+    def _attend(self, q: torch.Tensor, meta: SharedCacheAttnMetadata, layer_id: int, forked: bool = False) -> torch.Tensor:
+        """The attention of a planned step over keys that are already in the pool (``forked``: the
+        step's dense tiles were launched before the store and only have to be joined)."""
         if meta.phase == "prefill_batch":
             return self._forward_prefill_batch(q, meta, layer_id)
 
@@ -851,16 +882,20 @@ class SharedCacheAttention:
         status = self.status()
         plan: DecodePlan = meta.plan
         self._reserve_partials(plan.num_partials)
-        q2 = q.reshape(rows, -1)
-        if q2.stride(1) != 1:
-            q2 = q2.contiguous()
+        q2 = self._decode_queries(q, meta)
         out = torch.empty(rows, self.num_qo_heads * self.head_dim, dtype=q.dtype, device=q.device)
         pool = pool_struct(self.kv_cache, layer_id, self.num_qo_heads, self._cos_sin, self.rotary_dim)
-        rc = _lib.lib().va_view_decode(
-            C.byref(pool), C.byref(plan.struct), q2.data_ptr(), q2.stride(0), out.data_ptr(),
-            out.stride(0), self._partial_o.data_ptr(), self._partial_ml.data_ptr(),
-            status.data_ptr(), _lib.stream_ptr(),
-        )
+        mask = plan.struct.phase_mask
+        if forked:
+            plan.struct.phase_mask = mask | _lib.VA_PHASE_GROUPS_FORKED
+        try:
+            rc = _lib.lib().va_view_decode(
+                C.byref(pool), C.byref(plan.struct), q2.data_ptr(), q2.stride(0), out.data_ptr(),
+                out.stride(0), self._partial_o.data_ptr(), self._partial_ml.data_ptr(),
+                status.data_ptr(), _lib.stream_ptr(),
+            )
+        finally:
+            plan.struct.phase_mask = mask
         _lib.check(rc, "va_view_decode")
         return out
 

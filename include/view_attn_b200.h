@@ -106,6 +106,8 @@ int va_rope_rotate(const void* x, void* out, const int32_t* delta, int32_t n, in
 #define VA_PHASE_SKIP_STREAM 1 /* do not launch the streaming (partials) pass */
 #define VA_PHASE_SKIP_MERGE 2  /* do not launch the merge pass                */
 #define VA_PHASE_SKIP_GROUPS 4 /* do not launch the dense tiles of `groups`  */
+#define VA_PHASE_GROUPS_FORKED 8 /* va_view_decode_fork_groups launched the dense tiles of `groups` earlier on this
+                                    stream: join them before the merge pass, do not launch them again */
 
 struct VaDensePlan; /* section 4 */
 
@@ -140,6 +142,20 @@ int va_decode_lane_width(int32_t head_dim);
 int va_view_decode(const VaPool* pool, const VaDecodePlan* plan, const void* q,
                    int64_t q_row_stride, void* out, int64_t out_row_stride, float* partial_o,
                    float* partial_ml, int32_t* status, va_stream_t stream);
+
+/* The dense tiles of a decode step ahead of the rest.  The tiles of blocks that many requests read
+ * do not depend on this step's new keys unless one of those blocks is written in the step (the
+ * caller knows: a write target that is also a grouped block).  When they do not, the caller may
+ * launch them BEFORE it stores the new keys:
+ *     va_view_decode_fork_groups(...)   tiles forked from `stream` onto the library's side stream
+ *     va_store_kv(...)                  on `stream`
+ *     va_view_decode(...)               same plan with VA_PHASE_GROUPS_FORKED in phase_mask: the streaming
+ *                                       pass becomes resident under the store kernel (programmatic
+ *                                       dependent launch), the tiles are joined before the merge pass
+ * The reference has no counterpart (it runs its per-segment FlashInfer calls in order,
+ * shared_cache/attention.py:624-703); this only reorders launches of the same step. */
+int va_view_decode_fork_groups(const VaPool* pool, const VaDecodePlan* plan, const void* q, int64_t q_row_stride,
+                               float* partial_o, float* partial_ml, int32_t* status, va_stream_t stream);
 
 /* 4. Dense-tile view attention ----------------------------------------------------------------
  * Replaces: SharedCacheAttention._forward_prefill_batch shared_cache/attention.py:705-752 (the
