@@ -228,6 +228,9 @@ SIGNATURES = {
     "va_gdn_gated_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                        C.c_float, C.c_int32, C.c_int64, C.c_void_p]),
     "va_gdn_prefill_conv": (C.c_int, [C.POINTER(VaGdnPrefillConv), C.c_void_p]),
+    "va_add_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float,
+                                 C.c_int32, C.c_void_p]),
+    "va_silu_mul": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "va_attn_qk_norm": (C.c_int, [C.POINTER(VaAttnQkNorm), C.c_void_p]),
     "va_attn_output_gate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                       C.c_void_p]),

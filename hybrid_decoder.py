@@ -6,7 +6,8 @@ with a 2x-wide q projection (query + sigmoid output gate) and per-head q/k RMSNo
 layers Hk16 / Hv32 / dk = dv = 128 with a conv window of 4; SwiGLU MLP 12288; vocabulary 151 936; bf16.
 Weights are random (there are no checkpoints here), replicated on every GPU.
 
-Projections, MLP, layer norms and the LM head are plain torch GEMMs / elementwise ops; the attention
+Projections, MLP GEMMs and the LM head are plain torch GEMMs; the residual add + RMSNorm between
+sub-layers and the SwiGLU gate are ``decoder_glue.add_rmsnorm`` / ``silu_mul``; the attention
 layers are ``GatedAttentionLayer`` (q/k norm, ``SharedCacheAttention.forward``, output gate) and the
 GDN layers ``GatedDeltaNetLayer.forward_ar_decode``
 -- the kernels of this package -- and the whole decode forward is captured ONCE in a CUDA graph
@@ -30,6 +31,7 @@ import torch.nn.functional as F
 
 from async_llm_b200 import AsyncContext, CacheBlock, MHAKVCache, PageAllocator, SharedCacheAttention, WorkerGroup
 from async_llm_b200.attn_layer import GatedAttentionLayer
+from async_llm_b200.decoder_glue import add_rmsnorm, silu_mul
 from async_llm_b200.gdn_layer import GatedDeltaNetLayer
 from async_llm_b200.graph_io import SharedGraphIO
 from async_llm_b200.session_plan import plan_decode_writes
@@ -133,9 +135,6 @@ class HybridDecoder:
         self.norm_final = ones(h)
         self.lm_head = w(cfg.vocab, h)
 
-    def _norm(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-        return F.rms_norm(x, (x.shape[-1],), weight, self.cfg.eps)
-
     def forward(self, input_ids: torch.Tensor, batch, ar, timers: Optional[Dict[str, list]] = None) -> torch.Tensor:
         """Logits ``[rows, vocab]`` (fp32) of one decode step; ``batch`` carries the attention plan,
         ``ar`` the prepared GDN seam object.  ``timers`` (eager runs only) collects one CUDA-event pair
@@ -150,19 +149,18 @@ class HybridDecoder:
             timers.setdefault(kind, []).append((e0, e1))
             return out
 
-        def mlp(layer, h):
-            x = self._norm(h, layer.norm_post)
-            gate, up = F.linear(x, layer.w_gate_up).chunk(2, dim=-1)
-            return F.linear(F.silu(gate) * up, layer.w_down)
-
-        h = self.embed[input_ids.long()]
-        for layer in self.layers:
+        eps = self.cfg.eps
+        h = self.embed[input_ids.long()]      # the residual stream, updated in place by the fused add + norm
+        x = add_rmsnorm(h, None, self.layers[0].norm_in, eps)
+        for i, layer in enumerate(self.layers):
             if layer.kind == "attn":
-                h = h + timed("attn", lambda: layer.attn.forward(self._norm(h, layer.norm_in), batch))
+                a = timed("attn", lambda: layer.attn.forward(x, batch))
             else:
-                h = h + timed("gdn", lambda: layer.gdn.forward_ar_decode(self._norm(h, layer.norm_in), ar))
-            h = h + timed("mlp", lambda: mlp(layer, h))
-        return timed("head", lambda: F.linear(self._norm(h, self.norm_final), self.lm_head).float())
+                a = timed("gdn", lambda: layer.gdn.forward_ar_decode(x, ar))
+            x = add_rmsnorm(h, a, layer.norm_post, eps)
+            m = timed("mlp", lambda: F.linear(silu_mul(F.linear(x, layer.w_gate_up)), layer.w_down))
+            x = add_rmsnorm(h, m, self.layers[i + 1].norm_in if i + 1 < len(self.layers) else self.norm_final, eps)
+        return timed("head", lambda: F.linear(x, self.lm_head).float())
 
 
 class HybridSession:

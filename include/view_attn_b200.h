@@ -586,6 +586,19 @@ int va_attn_qk_norm(const VaAttnQkNorm* args, va_stream_t stream);
 int va_attn_output_gate(const void* o, const void* qkv, int64_t qkv_row_stride, void* out, int32_t n,
                         int32_t num_q_heads, int32_t head_dim, va_stream_t stream);
 
+/* 12. Decoder-layer glue (used by the full-model workload) ------------------------------------------
+ * va_add_rmsnorm replaces RMSNormFused.forward (layers/norm.py:25-43; FlashInfer
+ * `fused_add_rmsnorm` / `gemma_fused_add_rmsnorm`): residual <- residual + delta (fp32 sum, stored as
+ * bf16, in place), out <- sum * rsqrt(mean(sum^2) + eps) * (weight + (weight_plus_one ? 1 : 0)), one
+ * rounding.  delta NULL: no add (RMSNorm.forward, layers/norm.py:8-22).  All rows bf16 [n, dim]
+ * contiguous, weight bf16 [dim], dim a multiple of 8, at most 16384, 16-byte aligned pointers.
+ * va_silu_mul replaces silu_and_mul (layers/activation.py:9-12): out[n, inter] =
+ * bf16(silu(gate) * up), gate = columns [0, inter) and up = columns [inter, 2 inter) of rows
+ * row_stride elements apart; fp32 inside. */
+int va_add_rmsnorm(void* residual, const void* delta, const void* weight, void* out, int32_t n, int32_t dim,
+                   float eps, int32_t weight_plus_one, va_stream_t stream);
+int va_silu_mul(const void* gate_up, int64_t row_stride, void* out, int32_t n, int32_t inter, va_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -128,3 +128,28 @@ def test_graph_replay_after_replanning_into_fixed_buffers(cuda_device, dense_fra
         dv.attn.check_status()
         want, _, _ = oracle_decode(case)
         assert_close_bf16(out, want, "graph replay")
+
+
+def test_dense_tiles_launch_order_follows_what_the_step_writes(cuda_device):
+    # The tiles of a widely read block start before the step's keys are stored unless that block
+    # is itself written in the step: then its new key is one of the keys the tiles must see, and
+    # they stay behind the store.  Both orders give the oracle's rows.
+    lengths = {"shared": 700}
+    views, writes = [], []
+    for r in range(6):
+        lengths[f"p{r}"] = 40 + r
+        views.append(["shared", f"p{r}"])
+        writes.append(f"p{r}")
+    early = wl.make_view_case(lengths=lengths, views=views, writes=writes, num_q_heads=16, num_kv_heads=2,
+                              head_dim=256, page_size=16, rope_base=1e7, seed=21)
+    dv = wl.DeviceView(early, cuda_device)
+    batch = dv.plan()
+    assert batch.attn_metadata.plan.groups is not None and batch.attn_metadata.fork_dense_early
+    run_case(early, cuda_device)
+    # worker 0 appends to the block everybody reads
+    late = wl.make_view_case(lengths=lengths, views=views, writes=["shared"] + writes[1:], num_q_heads=16,
+                             num_kv_heads=2, head_dim=256, page_size=16, rope_base=1e7, seed=22)
+    dv = wl.DeviceView(late, cuda_device)
+    batch = dv.plan()
+    assert batch.attn_metadata.plan.groups is not None and not batch.attn_metadata.fork_dense_early
+    run_case(late, cuda_device)
