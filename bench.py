@@ -56,7 +56,7 @@ MIN_ROUNDS = 50
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernels of the default step, from the
 # committed ncu summary profiles/view_decode_config2_step_traffic.md (same command as this bench with
 # --kernel-only).  Only valid for the default workload; any other size reports traffic null.
-NCU_STEP_TRAFFIC = {"view_decode_stream_kernel": 269_845_000, "view_dense_tc_kernel": 17_441_000}
+NCU_STEP_TRAFFIC = {"view_decode_stream_kernel": 270_370_000, "view_dense_tc_kernel": 17_434_000}
 SIDE_WORKLOADS = ("prefill", "gdn_step", "gdn_prefill", "block_merge")
 
 
