@@ -631,6 +631,7 @@ def run_hybrid(device, steps: int, warmup: int, peaks, rank: int, world: int, pe
     # per-layer-type time of one eager forward (same kernels, launched one by one)
     timers = {}
     shards = partition_contexts(descs, world, sticky).shards[rank]
+    sess.forward_eager([contexts[i] for i in shards], [1] * len(shards))       # untimed: first-use allocations
     sess.forward_eager([contexts[i] for i in shards], [1] * len(shards), timers)
     torch.cuda.synchronize()
     by_type = {kind: sum(a.elapsed_time(b) for a, b in pairs) for kind, pairs in timers.items()}
