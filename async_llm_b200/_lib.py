@@ -102,6 +102,7 @@ class VaGdnPrefill(C.Structure):
         ("head_k_dim", C.c_int32), ("head_v_dim", C.c_int32), ("l2_eps", C.c_float), ("q_scale", C.c_float),
         ("engine", C.c_int32), ("max_segment_tokens", C.c_int32), ("scratch", C.c_void_p),
         ("scratch_bytes", C.c_int64), ("num_tokens", C.c_int64), ("summary_dtype", C.c_int32),
+        ("status", C.c_void_p),
     ]
 
 

@@ -17,6 +17,7 @@
 // row-wise from L2.  No GEMM, no state materialised, HBM traffic = read + write of the write
 // block's summary.
 #include "common.cuh"
+#include "tc05.cuh"
 
 namespace {
 
@@ -424,6 +425,7 @@ struct ScanParams {
   float* s_ed;           // [Hv][N] e^(gc_last - gc)
   int64_t num_tokens;
   int32_t summary_bf16;  // init_a/init_b/write_a/write_b name bf16 tensors (fp32 otherwise)
+  int32_t* status;       // device word for VA_DEV_* findings, or null
 };
 
 constexpr int kScanTokens = 16;  // tokens staged per pass
@@ -622,9 +624,8 @@ __device__ __forceinline__ void frag_b_kn(uint32_t (&b)[4], uint32_t base, int l
 // it once per (chunk, head, request), all chunks in parallel, and leaves K, Q, -W, U, P, e^gc and
 // e^(gc_last-gc) in the caller's scratch.  gdn_chunk_state_kernel then walks a part's chunks in
 // order with only the state-dependent products (Vnew = U - W X, O, the state update); the state X
-// stays in the accumulator registers of its four warps for the whole block (warp w owns rows
-// 32w..32w+31) and is rounded to bf16 into shared memory once per chunk as the B operand of W X
-// and Q X.
+// stays in the accumulator registers of its sixteen warps for the whole block (a 16 x 64 tile each)
+// and is rounded to bf16 into shared memory once per chunk as the B operand of W X and Q X.
 struct PreSmem {
   static constexpr int kKs = 0;
   static constexpr int kQs = kKs + kC * kLdD * 2;
@@ -884,29 +885,37 @@ __global__ void __launch_bounds__(128, 2) gdn_chunk_pre_kernel(const __grid_cons
 }
 
 struct StateSmem {
-  static constexpr int kKs = 0;                                   // K    [C][dk]
-  static constexpr int kWs = kKs + kC * kLdD * 2;                 // -W   [C][dk]
-  static constexpr int kUs = kWs + kC * kLdD * 2;                 // U    [C][128]
-  static constexpr int kQs = kUs + kC * kLdD * 2;                 // Q    [C][dk]     (part 0)
-  static constexpr int kVn = kQs + kC * kLdD * 2;                 // Vnew [C][128]    (part 0)
-  static constexpr int kVd = kVn + kC * kLdD * 2;                 // diag(e^(gc_last-gc)) Vnew
-  static constexpr int kXs = kVd + kC * kLdD * 2;                 // X    [dk][128] bf16
+  // K, -W and U of a chunk are fetched one chunk ahead into two alternating buffers; Q and P (part 0)
+  // are fetched at the start of their chunk and are not needed before its second product
+  static constexpr int kTile = kC * kLdD * 2;                     // one [C][128] bf16 tile
+  static constexpr int kKs = 0;                                   // K    [2][C][dk]
+  static constexpr int kWs = kKs + 2 * kTile;                     // -W   [2][C][dk]
+  static constexpr int kUs = kWs + 2 * kTile;                     // U    [2][C][128]
+  static constexpr int kQs = kUs + 2 * kTile;                     // Q    [C][dk]     (part 0)
+  static constexpr int kVn = kQs + kTile;                         // Vnew [C][128]    (part 0)
+  static constexpr int kVd = kVn + kTile;                         // diag(e^(gc_last-gc)) Vnew
+  static constexpr int kXs = kVd + kTile;                         // X    [dk][128] bf16
   static constexpr int kPs = kXs + kD * kLdD * 2;                 // P    [C][C]      (part 0)
-  static constexpr int kVec = kPs + kC * kLdC * 2;                // e^gc, e^(gc_last-gc)
-  static constexpr int kTotal = kVec + 2 * kC * 4;
+  static constexpr int kVec = kPs + kC * kLdC * 2;                // [2][e^gc, e^(gc_last-gc)]
+  static constexpr int kTotal = kVec + 2 * 2 * kC * 4;
+  static_assert(kTotal <= 227 * 1024, "shared memory of the chunk state kernel");
 };
 
-// grid (3, Hv, R), 128 threads: one part of the joint state, chunks in order
-__global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_constant__ ScanParams p) {
+// grid (3, Hv, R), 512 threads: one part of the joint state, chunks in order.  Sixteen warps, four
+// per scheduler: the chunk's products are chains of ldmatrix -> mma.sync -> shared-memory hand-offs,
+// and with one warp per scheduler (an earlier version: four warps owning 32 state rows each) every
+// dependent instruction stalled the SM -- the tensor pipe was busy 34 % of the time.
+//   state tile of warp w: rows 16 (w & 7) .., columns 64 (w >> 3) ..   (X update, 8 n-tiles)
+//   token tile of warp w: rows 16 (w & 3) .., columns 32 (w >> 2) ..   (Vnew and O, 4 n-tiles)
+constexpr int kStateThreads = 512;
+__global__ void __launch_bounds__(kStateThreads, 1) gdn_chunk_state_kernel(const __grid_constant__ ScanParams p) {
   extern __shared__ __align__(128) unsigned char csm[];
   using Sm = StateSmem;
   const uint32_t sb = smem_u32(csm);
-  __nv_bfloat16* Us = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kUs);
   __nv_bfloat16* Vn = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kVn);
   __nv_bfloat16* Vd = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kVd);
   __nv_bfloat16* Xs = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kXs);
-  float* eg = reinterpret_cast<float*>(csm + Sm::kVec);
-  float* ed = eg + kC;
+  float* vec = reinterpret_cast<float*>(csm + Sm::kVec);
   const int part = blockIdx.x;
   const int h = blockIdx.y;
   const int r = blockIdx.z;
@@ -915,12 +924,14 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
   const int lane = tid & 31;
   const int g = lane >> 2;
   const int t = lane & 3;
+  const int srow = 16 * (warp & 7), scol = 64 * (warp >> 3);   // state tile
+  const int trow = 16 * (warp & 3), tcol = 32 * (warp >> 2);   // token tile
   const int t_begin = p.seg_off[r];
   const int t_end = p.seg_off[r + 1];
   const int64_t head_off = static_cast<int64_t>(h) * kD * kD;
   const int64_t hN = static_cast<int64_t>(h) * p.num_tokens;
 
-  float acc[2][16][4];
+  float acc[8][4];
   {
     const void* src = nullptr;   // part 0: fp32 state; parts 1, 2: a summary in its storage type
     int64_t src_off = 0;
@@ -937,17 +948,14 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
       transposed = true;
     }
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
+    for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = 32 * warp + 16 * mt + g + (e >> 1) * 8;
-          const int col = 8 * nt + 2 * t + (e & 1);
-          float x = (part == 1 && row == col) ? 1.f : 0.f;
-          if (src != nullptr) x = sum_ld1(src, src_off + (transposed ? col * kD + row : row * kD + col), sum_bf16);
-          acc[mt][nt][e] = x;
-        }
+      for (int e = 0; e < 4; ++e) {
+        const int row = srow + g + (e >> 1) * 8;
+        const int col = scol + 8 * nt + 2 * t + (e & 1);
+        float x = (part == 1 && row == col) ? 1.f : 0.f;
+        if (src != nullptr) x = sum_ld1(src, src_off + (transposed ? col * kD + row : row * kD + col), sum_bf16);
+        acc[nt][e] = x;
       }
     }
   }
@@ -955,50 +963,62 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
   // one row of a [C][128] bf16 tile = 256 bytes = 16 copies of 16 bytes; 64 rows x 16 = 1024 per tile
   auto load_tile = [&](uint32_t dst, const __nv_bfloat16* src, int t0, int row_elems, int ld) {
     const int per_row = row_elems / 8;
-    for (int idx = tid; idx < kC * per_row; idx += 128) {
+    for (int idx = tid; idx < kC * per_row; idx += kStateThreads) {
       const int i = idx / per_row, c = idx - i * per_row;
       const bool live = t0 + i < t_end;
       cp_async16(dst + (i * ld + c * 8) * 2, src + (hN + (live ? t0 + i : t0)) * row_elems + c * 8, live ? 16 : 0);
     }
   };
-
-  for (int t0 = t_begin; t0 < t_end; t0 += kC) {
-    __syncthreads();   // the previous chunk's tiles are no longer read
-    load_tile(sb + Sm::kKs, p.s_k, t0, kD, kLdD);
-    load_tile(sb + Sm::kWs, p.s_w, t0, kD, kLdD);
-    if (part != 1) load_tile(sb + Sm::kUs, p.s_u, t0, kD, kLdD);
+  // K, -W, U and the decay vectors of the chunk at t0 into buffer `buf`
+  auto prefetch = [&](int t0, int buf) {
+    if (t0 < t_end) {
+      load_tile(sb + Sm::kKs + buf * Sm::kTile, p.s_k, t0, kD, kLdD);
+      load_tile(sb + Sm::kWs + buf * Sm::kTile, p.s_w, t0, kD, kLdD);
+      if (part != 1) load_tile(sb + Sm::kUs + buf * Sm::kTile, p.s_u, t0, kD, kLdD);
+      if (tid < kC) {
+        const bool live = t0 + tid < t_end;
+        vec[buf * 2 * kC + tid] = live ? p.s_eg[hN + t0 + tid] : 0.f;
+        vec[buf * 2 * kC + kC + tid] = live ? p.s_ed[hN + t0 + tid] : 0.f;
+      }
+    }
+    cp_async_commit();   // (an empty group past the last chunk keeps the group count uniform)
+  };
+  prefetch(t_begin, 0);
+  int buf = 0;
+  for (int t0 = t_begin; t0 < t_end; t0 += kC, buf ^= 1) {
+    __syncthreads();   // the previous chunk's tiles (and the other buffer) are no longer read
     if (part == 0) {
       load_tile(sb + Sm::kQs, p.s_q, t0, kD, kLdD);
       load_tile(sb + Sm::kPs, p.s_p, t0, kC, kLdC);
     }
     cp_async_commit();
-    if (tid < kC) {
-      const bool live = t0 + tid < t_end;
-      eg[tid] = live ? p.s_eg[hN + t0 + tid] : 0.f;
-      ed[tid] = live ? p.s_ed[hN + t0 + tid] : 0.f;
-    }
-    // ---- X as a bf16 B operand (every warp writes its 32 rows) while the copies are in flight
+    prefetch(t0 + kC, buf ^ 1);
+    const uint32_t Kb = sb + Sm::kKs + buf * Sm::kTile;
+    const uint32_t Wb = sb + Sm::kWs + buf * Sm::kTile;
+    const __nv_bfloat16* Us = reinterpret_cast<const __nv_bfloat16*>(csm + Sm::kUs + buf * Sm::kTile);
+    const float* eg = vec + buf * 2 * kC;
+    const float* ed = eg + kC;
+    // ---- X as a bf16 B operand (every warp writes its state tile) while the copies are in flight
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-#pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-        const int row = 32 * warp + 16 * mt + g;
-        *reinterpret_cast<uint32_t*>(Xs + row * kLdD + 8 * nt + 2 * t) = pack_bf16(acc[mt][nt][0], acc[mt][nt][1]);
-        *reinterpret_cast<uint32_t*>(Xs + (row + 8) * kLdD + 8 * nt + 2 * t) = pack_bf16(acc[mt][nt][2], acc[mt][nt][3]);
-      }
+    for (int nt = 0; nt < 8; ++nt) {
+      const int row = srow + g;
+      const int col = scol + 8 * nt + 2 * t;
+      *reinterpret_cast<uint32_t*>(Xs + row * kLdD + col) = pack_bf16(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<uint32_t*>(Xs + (row + 8) * kLdD + col) = pack_bf16(acc[nt][2], acc[nt][3]);
     }
-    cp_async_wait<0>();
+    cp_async_wait<2>();   // this chunk's K, -W, U (fetched during the previous chunk) have landed
     __syncthreads();
 
-    // ---- Vnew = U - W X for this warp's 16 token rows
-    float vn[16][4];
+    // ---- Vnew = U - W X for this warp's token tile (16 tokens x 32 columns)
+    float vn[4][4];
     {
-      const int i = 16 * warp + g;
+      const int i = trow + g;
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
         if (part != 1) {
-          const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(Us + i * kLdD + 8 * nt + 2 * t));
-          const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(Us + (i + 8) * kLdD + 8 * nt + 2 * t));
+          const int col = tcol + 8 * nt + 2 * t;
+          const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(Us + i * kLdD + col));
+          const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(Us + (i + 8) * kLdD + col));
           vn[nt][0] = lo.x;
           vn[nt][1] = lo.y;
           vn[nt][2] = hi.x;
@@ -1011,56 +1031,58 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
 #pragma unroll
     for (int ks = 0; ks < kD / 16; ++ks) {
       uint32_t a[4];
-      frag_a(a, sb + Sm::kWs, kLdD, 16 * warp, 16 * ks, lane);
+      frag_a(a, Wb, kLdD, trow, 16 * ks, lane);
 #pragma unroll
-      for (int np = 0; np < 8; ++np) {
+      for (int np = 0; np < 2; ++np) {
         uint32_t b[4];
-        frag_b_kn(b, sb + Sm::kXs, kLdD, 16 * ks, 16 * np, lane);
+        frag_b_kn(b, sb + Sm::kXs, kLdD, 16 * ks, tcol + 16 * np, lane);
         const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
         mma_bf16_16816(vn[2 * np], a, b0);
         mma_bf16_16816(vn[2 * np + 1], a, b1);
       }
     }
     {
-      const int i = 16 * warp + g;
+      const int i = trow + g;
       const float d0 = ed[i], d1 = ed[i + 8];
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
+        const int col = tcol + 8 * nt + 2 * t;
         if (part == 0) {
-          *reinterpret_cast<uint32_t*>(Vn + i * kLdD + 8 * nt + 2 * t) = pack_bf16(vn[nt][0], vn[nt][1]);
-          *reinterpret_cast<uint32_t*>(Vn + (i + 8) * kLdD + 8 * nt + 2 * t) = pack_bf16(vn[nt][2], vn[nt][3]);
+          *reinterpret_cast<uint32_t*>(Vn + i * kLdD + col) = pack_bf16(vn[nt][0], vn[nt][1]);
+          *reinterpret_cast<uint32_t*>(Vn + (i + 8) * kLdD + col) = pack_bf16(vn[nt][2], vn[nt][3]);
         }
-        *reinterpret_cast<uint32_t*>(Vd + i * kLdD + 8 * nt + 2 * t) = pack_bf16(vn[nt][0] * d0, vn[nt][1] * d0);
-        *reinterpret_cast<uint32_t*>(Vd + (i + 8) * kLdD + 8 * nt + 2 * t) = pack_bf16(vn[nt][2] * d1, vn[nt][3] * d1);
+        *reinterpret_cast<uint32_t*>(Vd + i * kLdD + col) = pack_bf16(vn[nt][0] * d0, vn[nt][1] * d0);
+        *reinterpret_cast<uint32_t*>(Vd + (i + 8) * kLdD + col) = pack_bf16(vn[nt][2] * d1, vn[nt][3] * d1);
       }
     }
+    cp_async_wait<1>();   // this chunk's Q and P have landed (the next chunk's tiles may still be in flight)
     __syncthreads();
 
-    // ---- O = diag(e^gc) (Q X) + P Vnew for this warp's 16 token rows (part 0 only)
+    // ---- O = diag(e^gc) (Q X) + P Vnew for this warp's token tile (part 0 only)
     if (part == 0) {
-      float o[16][4];
+      float o[4][4];
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
       }
 #pragma unroll
       for (int ks = 0; ks < kD / 16; ++ks) {
         uint32_t a[4];
-        frag_a(a, sb + Sm::kQs, kLdD, 16 * warp, 16 * ks, lane);
+        frag_a(a, sb + Sm::kQs, kLdD, trow, 16 * ks, lane);
 #pragma unroll
-        for (int np = 0; np < 8; ++np) {
+        for (int np = 0; np < 2; ++np) {
           uint32_t b[4];
-          frag_b_kn(b, sb + Sm::kXs, kLdD, 16 * ks, 16 * np, lane);
+          frag_b_kn(b, sb + Sm::kXs, kLdD, 16 * ks, tcol + 16 * np, lane);
           const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
           mma_bf16_16816(o[2 * np], a, b0);
           mma_bf16_16816(o[2 * np + 1], a, b1);
         }
       }
-      const int i = 16 * warp + g;
+      const int i = trow + g;
       const float e0 = eg[i], e1 = eg[i + 8];
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
         o[nt][0] *= e0;
         o[nt][1] *= e0;
         o[nt][2] *= e1;
@@ -1069,11 +1091,11 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
 #pragma unroll
       for (int ks = 0; ks < kC / 16; ++ks) {
         uint32_t a[4];
-        frag_a(a, sb + Sm::kPs, kLdC, 16 * warp, 16 * ks, lane);
+        frag_a(a, sb + Sm::kPs, kLdC, trow, 16 * ks, lane);
 #pragma unroll
-        for (int np = 0; np < 8; ++np) {
+        for (int np = 0; np < 2; ++np) {
           uint32_t b[4];
-          frag_b_kn(b, sb + Sm::kVn, kLdD, 16 * ks, 16 * np, lane);
+          frag_b_kn(b, sb + Sm::kVn, kLdD, 16 * ks, tcol + 16 * np, lane);
           const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
           mma_bf16_16816(o[2 * np], a, b0);
           mma_bf16_16816(o[2 * np + 1], a, b1);
@@ -1081,42 +1103,36 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
       }
       const int64_t tok0 = static_cast<int64_t>(t0) + i;
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
+        const int col = tcol + 8 * nt + 2 * t;
         if (tok0 < t_end)
-          *reinterpret_cast<uint32_t*>(p.out + (tok0 * p.num_v_heads + h) * kD + 8 * nt + 2 * t) =
-              pack_bf16(o[nt][0], o[nt][1]);
+          *reinterpret_cast<uint32_t*>(p.out + (tok0 * p.num_v_heads + h) * kD + col) = pack_bf16(o[nt][0], o[nt][1]);
         if (tok0 + 8 < t_end)
-          *reinterpret_cast<uint32_t*>(p.out + ((tok0 + 8) * p.num_v_heads + h) * kD + 8 * nt + 2 * t) =
+          *reinterpret_cast<uint32_t*>(p.out + ((tok0 + 8) * p.num_v_heads + h) * kD + col) =
               pack_bf16(o[nt][2], o[nt][3]);
       }
     }
 
-    // ---- X <- e^gc_last X + K^T (diag(e^(gc_last - gc)) Vnew) for this warp's 32 state rows
+    // ---- X <- e^gc_last X + K^T (diag(e^(gc_last - gc)) Vnew) for this warp's state tile
     {
       const int n_live = min(kC, t_end - t0);
       const float tail = eg[n_live - 1];   // tokens past the end do not decay the state
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
+      for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[mt][nt][e] *= tail;
-        }
+        for (int e = 0; e < 4; ++e) acc[nt][e] *= tail;
       }
 #pragma unroll
       for (int ks = 0; ks < kC / 16; ++ks) {
-        uint32_t a0[4], a1[4];
-        frag_a_t(a0, sb + Sm::kKs, kLdD, 32 * warp, 16 * ks, lane);
-        frag_a_t(a1, sb + Sm::kKs, kLdD, 32 * warp + 16, 16 * ks, lane);
+        uint32_t a0[4];
+        frag_a_t(a0, Kb, kLdD, srow, 16 * ks, lane);
 #pragma unroll
-        for (int np = 0; np < 8; ++np) {
+        for (int np = 0; np < 4; ++np) {
           uint32_t b[4];
-          frag_b_kn(b, sb + Sm::kVd, kLdD, 16 * ks, 16 * np, lane);
+          frag_b_kn(b, sb + Sm::kVd, kLdD, 16 * ks, scol + 16 * np, lane);
           const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
-          mma_bf16_16816(acc[0][2 * np], a0, b0);
-          mma_bf16_16816(acc[0][2 * np + 1], a0, b1);
-          mma_bf16_16816(acc[1][2 * np], a1, b0);
-          mma_bf16_16816(acc[1][2 * np + 1], a1, b1);
+          mma_bf16_16816(acc[2 * np], a0, b0);
+          mma_bf16_16816(acc[2 * np + 1], a0, b1);
         }
       }
     }
@@ -1140,20 +1156,19 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_state_kernel(const __grid_co
     }
     if (dst != nullptr) {
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
+      for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int row = 32 * warp + 16 * mt + g + (e >> 1) * 8;
-            const int col = 8 * nt + 2 * t + (e & 1);
-            sum_st1(dst, dst_off + (transposed ? col * kD + row : row * kD + col), acc[mt][nt][e], sum_bf16);
-          }
+        for (int e = 0; e < 4; ++e) {
+          const int row = srow + g + (e >> 1) * 8;
+          const int col = scol + 8 * nt + 2 * t + (e & 1);
+          sum_st1(dst, dst_off + (transposed ? col * kD + row : row * kD + col), acc[nt][e], sum_bf16);
         }
       }
     }
   }
 }
+
+#include "gdn_chunk_tc.cuh"
 
 int check_gdn_dims(int num_k_heads, int num_v_heads, int dk, int dv) {
   if (dk != kD || dv != kD) return VA_ERR_UNSUPPORTED;
@@ -1282,9 +1297,11 @@ extern "C" int va_gdn_prefill(const VaGdnPrefill* a, va_stream_t stream) {
   p.num_tokens = 0;
   if (a->summary_dtype != VA_SUMMARY_F32 && a->summary_dtype != VA_SUMMARY_BF16) return VA_ERR_BAD_ARG;
   p.summary_bf16 = a->summary_dtype == VA_SUMMARY_BF16;
+  p.status = a->status;
   dim3 grid(3, a->num_v_heads, a->num_requests);
   cudaError_t e;
-  if (a->engine == VA_GDN_ENGINE_CHUNK && a->scratch != nullptr) {
+  const bool chunked = a->engine == VA_GDN_ENGINE_CHUNK || a->engine == VA_GDN_ENGINE_CHUNK_TC;
+  if (chunked && a->scratch != nullptr) {
     // two passes: the state-independent half of every chunk in parallel, then the states in order
     if (a->num_tokens <= 0 || a->scratch_bytes < va_gdn_prefill_scratch_bytes(a->num_tokens, a->num_v_heads) ||
         (reinterpret_cast<uintptr_t>(a->scratch) & 15))
@@ -1305,11 +1322,16 @@ extern "C" int va_gdn_prefill(const VaGdnPrefill* a, va_stream_t stream) {
     if (e != cudaSuccess) return va_host::note_cuda_error(e);
     e = cudaFuncSetAttribute(gdn_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, StateSmem::kTotal);
     if (e != cudaSuccess) return va_host::note_cuda_error(e);
+    e = cudaFuncSetAttribute(gdn_chunk_state_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcStateSmem::kTotal);
+    if (e != cudaSuccess) return va_host::note_cuda_error(e);
     gdn_chunk_pre_kernel<<<pre_grid, 128, PreSmem::kTotal, static_cast<cudaStream_t>(stream)>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return va_host::note_cuda_error(e);
-    gdn_chunk_state_kernel<<<grid, 128, StateSmem::kTotal, static_cast<cudaStream_t>(stream)>>>(p);
-  } else if (a->engine == VA_GDN_ENGINE_CHUNK) {
+    if (a->engine == VA_GDN_ENGINE_CHUNK_TC)
+      gdn_chunk_state_tc_kernel<<<grid, kTcStateThreads, TcStateSmem::kTotal, static_cast<cudaStream_t>(stream)>>>(p);
+    else
+      gdn_chunk_state_kernel<<<grid, kStateThreads, StateSmem::kTotal, static_cast<cudaStream_t>(stream)>>>(p);
+  } else if (chunked) {
     return VA_ERR_BAD_ARG;   // the chunk engine needs its scratch
   } else if (a->engine == VA_GDN_ENGINE_SCAN) {
     gdn_scan_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);

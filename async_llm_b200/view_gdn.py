@@ -32,7 +32,7 @@ import torch
 from . import _lib
 from .blocks import CacheBlock, _TrackedDict
 
-GDN_ENGINES = {"scan": 0, "chunk": 1}   # VA_GDN_ENGINE_* of the C header
+GDN_ENGINES = {"scan": 0, "chunk": 1, "chunk_tc": 2}   # VA_GDN_ENGINE_* of the C header
 
 
 # rows of the per-step address table [8, layers, workers, depth]
@@ -150,12 +150,14 @@ class SharedCacheGDN:
         if state_dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("Shared GDN state dtype must be float32 or bfloat16")
         self._summary_code = _lib.summary_code(state_dtype)
-        # fused prefill: "chunk" = 64-token chunks on the tensor cores (bf16 operands, fp32 state),
-        # "scan" = token-by-token fp32 recurrence (also what capture_token_affines always runs)
-        self.prefill_engine = prefill_engine or os.environ.get("VIEWATTN_GDN_ENGINE", "chunk")
+        # fused prefill: "chunk_tc" = 64-token chunks, the state walked with tcgen05 products (state in
+        # TMEM; bf16 operands, fp32 state), "chunk" = the same on mma.sync, "scan" = token-by-token
+        # fp32 recurrence (also what capture_token_affines always runs)
+        self.prefill_engine = prefill_engine or os.environ.get("VIEWATTN_GDN_ENGINE", "chunk_tc")
         if self.prefill_engine not in GDN_ENGINES:
             raise ValueError(f"prefill_engine must be one of {sorted(GDN_ENGINES)}")
         self._chunk_scratch: Optional[torch.Tensor] = None
+        self._status: Optional[torch.Tensor] = None
         self._init_row_index: Optional[torch.Tensor] = None
         self.decode_buffers: Optional[GDNDecodeBuffers] = None
         self.prefill_buffers: Optional[GDNPrefillBuffers] = None
@@ -175,6 +177,20 @@ class SharedCacheGDN:
         self._step = None      # tables + outputs of the prepared forward
         self._pending = []     # (event, references) kept until the GPU is done with raw pointers
         self.prepare_count = 0
+
+    def status(self) -> torch.Tensor:
+        """Device word the kernels report findings into (a bounded wait that ran out)."""
+        if self._status is None:
+            self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._status
+
+    def check_status(self) -> None:
+        """Raise if a kernel of this object reported a device-side finding (synchronises)."""
+        if self._status is not None:
+            code = int(self._status.item())
+            if code:
+                self._status.zero_()
+                raise RuntimeError(f"GDN kernel reported device status {code}")
 
     # ------------------------------------------------------------------ context
     def set_context(self, cache_structure, write_to, prefill_segments=None) -> None:
@@ -615,11 +631,12 @@ class SharedCacheGDN:
         a.l2_eps, a.q_scale = eps, self.head_k_dim ** -0.5
         a.engine = GDN_ENGINES[engine]
         a.summary_dtype = self._summary_code
+        a.status = self.status().data_ptr()
         a.num_tokens = N
         a.max_segment_tokens = (int(max(segments)) if len(segments) else 0) if buffers is None else N
-        if engine == "chunk" and buffers is not None:
+        if engine != "scan" and buffers is not None:
             a.scratch, a.scratch_bytes = buffers.scratch.data_ptr(), buffers.scratch.numel()
-        elif engine == "chunk" and N > 0:
+        elif engine != "scan" and N > 0:
             # scratch of the chunk pre-pass (K, Q, -W, U, P rows per token and head), kept and grown
             need = int(_lib.lib().va_gdn_prefill_scratch_bytes(N, self.num_heads))
             if self._chunk_scratch is None or self._chunk_scratch.numel() < need:

@@ -274,16 +274,21 @@ def time_graph(fn, iters: int, device) -> float:
 
 
 def time_plain(fn, iters: int) -> float:
-    """Milliseconds per call of ``fn`` launched back to back (for calls far longer than a launch)."""
-    fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
+    """Median milliseconds per call of ``fn`` (for calls far longer than a launch): three untimed calls
+    (first-use allocations, the caching allocator's pool), then every call timed by its own pair of
+    CUDA events."""
+    for _ in range(3):
         fn()
-    e1.record()
-    e1.synchronize()
-    return e0.elapsed_time(e1) / iters
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(max(iters, 5)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
 
 
 def timed_cpu(fn, repeats: int = 1) -> float:
@@ -474,7 +479,7 @@ def side_gdn_prefill(device, iters, peaks, with_cpu):
 
     ms = time_plain(four_blocks, max(2, iters // 4))
     tokens = R * T * NB
-    chunked = ar.prefill_engine == "chunk"
+    chunked = ar.prefill_engine != "scan"
     # Per 64-token chunk and value head.  Pre-pass, computed ONCE for the three parts of the joint
     # state [S | A_hat | B_hat]: K K^T and Q K^T (64x64x128 each), W = T K' and U = T V' (64x128x64
     # each) plus the triangular inverse.  State pass, once per PART: W X (64x128x128) and

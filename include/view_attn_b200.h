@@ -302,19 +302,24 @@ typedef struct VaGdnPrefill {
    * va_gdn_prefill_scratch_bytes(num_tokens, num_v_heads)): the state-independent half of every
    * chunk (normalised K and Q, W, U, the causal score tile, the decays) is computed once, all
    * chunks in parallel, and parked there before the three states are walked in order.
-   * Required by VA_GDN_ENGINE_CHUNK, ignored by VA_GDN_ENGINE_SCAN. */
+   * Required by VA_GDN_ENGINE_CHUNK and VA_GDN_ENGINE_CHUNK_TC, ignored by VA_GDN_ENGINE_SCAN. */
   int32_t max_segment_tokens; /* longest request, 0 = unknown (num_tokens is used)  */
   void* scratch;
   int64_t scratch_bytes;
   int64_t num_tokens;       /* N (rows of q/k/v); needed with scratch              */
   int32_t summary_dtype;    /* VA_SUMMARY_*: storage type of init_a/b and write_a/b */
+  int32_t* status;          /* device word for VA_DEV_* findings (a bounded wait of the CHUNK_TC
+                               engine that ran out), or NULL                                       */
 } VaGdnPrefill;
 
 /* SCAN: token by token in fp32 (exact restatement of the recurrence, state in registers).
  * CHUNK: 64 tokens at a time on the tensor cores (UT transform of _chunk_gated_delta_rule,
- * models/qwen3_5_delta.py:85-114): bf16 operands, fp32 accumulation and fp32 state. */
+ * models/qwen3_5_delta.py:85-114): bf16 operands, fp32 accumulation and fp32 state; mma.sync.
+ * CHUNK_TC: the same chunk pre-pass, the state walked with tcgen05 products (state resident in
+ * TMEM, transposed so that the 128 feature rows are the M dimension). */
 #define VA_GDN_ENGINE_SCAN 0
 #define VA_GDN_ENGINE_CHUNK 1
+#define VA_GDN_ENGINE_CHUNK_TC 2
 
 int64_t va_gdn_prefill_scratch_bytes(int64_t num_tokens, int32_t num_v_heads);
 int va_gdn_prefill(const VaGdnPrefill* args, va_stream_t stream);

@@ -134,7 +134,7 @@ def test_fused_decode_step_bf16_summaries(cuda_device):
         assert_same_rounding(Bm, want_new[w][1], f"worker {w} B_hat")
 
 
-@pytest.mark.parametrize("engine", ["scan", "chunk"])
+@pytest.mark.parametrize("engine", ["scan", "chunk", "chunk_tc"])
 def test_prefill_bf16_summaries(cuda_device, engine):
     # two blocks written in order: the second starts from the (bf16) summary of the first; outputs
     # against one uninterrupted scan, summaries against the oracle's rounded capture
@@ -159,6 +159,7 @@ def test_prefill_bf16_summaries(cuda_device, engine):
         o = ar.prefill_scan(0, *(t.to(cuda_device) for t in data[j]))
         ar.finish_prefill(True)
         torch.cuda.synchronize()
+        ar.check_status()
         outs.append(o.cpu())
         written.append(new)
     q, k, v, gate, beta = (torch.cat([d[i] for d in data]) for i in range(5))

@@ -109,7 +109,7 @@ def test_compose_and_capture_reference_sequence(cuda_device):
     assert ar.compose_initial_recurrent_state(1, torch.float32) is None
 
 
-@pytest.mark.parametrize("engine", ["scan", "chunk"])
+@pytest.mark.parametrize("engine", ["scan", "chunk", "chunk_tc"])
 def test_prefill_scan_carries_state_across_blocks(cuda_device, engine):
     # three blocks written in order by two requests: block j starts from the fold of blocks < j,
     # so the outputs equal one uninterrupted scan, and every block gets its own summary
@@ -130,6 +130,7 @@ def test_prefill_scan_carries_state_across_blocks(cuda_device, engine):
         o = ar.prefill_scan(0, *cat)
         ar.finish_prefill(True)
         torch.cuda.synchronize()
+        ar.check_status()
         for r in range(R):
             outs[r].append(o[r * T: (r + 1) * T].cpu())
             written[r].append(new[r])
@@ -171,7 +172,7 @@ MULTI_CHUNK_SHAPES = {
 }
 
 
-@pytest.mark.parametrize("engine", ["scan", "chunk"])
+@pytest.mark.parametrize("engine", ["scan", "chunk", "chunk_tc"])
 @pytest.mark.parametrize("shape", list(MULTI_CHUNK_SHAPES))
 def test_prefill_blocks_of_many_chunks(cuda_device, engine, shape):
     # Blocks far longer than one 64-token chunk: inside a launch the chunked engine carries the state
@@ -193,6 +194,7 @@ def test_prefill_blocks_of_many_chunks(cuda_device, engine, shape):
         o = ar.prefill_scan(0, *cat)
         ar.finish_prefill(True)
         torch.cuda.synchronize()
+        ar.check_status()
         for r in range(R):
             outs[r].append(o[r * T: (r + 1) * T].cpu())
             written[r].append(new[r])

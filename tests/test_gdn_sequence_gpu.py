@@ -64,7 +64,7 @@ def check_blocks(a, c):
                                atol=1e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("engine", ["chunk", "scan"])
+@pytest.mark.parametrize("engine", ["chunk_tc", "chunk", "scan"])
 def test_layer_sequence_matches_reference_layer(cuda_device, engine):
     layer, ar, x = build(cuda_device, engine)
     s, a, b, c = (CacheBlock(cuda_device, 16) for _ in range(4))
@@ -92,7 +92,7 @@ def test_layer_sequence_replayed_from_graphs_with_fixed_buffers(cuda_device):
     # the same sequence with every forward replayed from a CUDA graph captured ONCE on a dummy topology:
     # the step's addresses are planned into fixed-capacity tables (more workers / rows / depth than any
     # step uses), inputs are staged into fixed rows, padding rows and requests publish nothing
-    layer, ar, x = build(cuda_device, "chunk")
+    layer, ar, x = build(cuda_device, "chunk_tc")
     CAP_W, CAP_ROWS, DEPTH = 4, 160, 3
     dec = GDNDecodeBuffers(ar, 1, CAP_W, DEPTH, torch.bfloat16)
     pre = GDNPrefillBuffers(ar, 1, CAP_W, DEPTH, torch.bfloat16, CAP_ROWS)
