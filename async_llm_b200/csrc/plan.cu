@@ -427,3 +427,81 @@ extern "C" int va_plan_views(const VaPlanParams* params, const VaViewStep* step,
                         s.key.data(), s.pages.data(), static_cast<int32_t>(s.pages.size()), blob, blob_words,
                         layout);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Tile table of a batched view-conditioned prefill (host code, no CUDA call).
+//
+// Request r owns output rows [row_offset, row_offset + num_new) and the segment rows
+// [seg_begin, seg_begin + seg_count) of `segments` (8 words each: page run, token begin, keys,
+// query rotation base, causal base or -1, ...).  Its new tokens are cut into tiles of `per_tile`
+// consecutive tokens; every (request, token tile, kv head) is one row of `tiles` (8 words:
+// entry_begin, entry_count, seg_begin, seg_count, kv head, 0, 0, 0).  Rows are ordered heaviest
+// first (cost = keys the tile walks x its rows; a causal segment is walked up to the last key the
+// tile's last row sees; ties keep request / token / head order) and every other round of `num_ctas`
+// rows is reversed, so that the CTA that takes rows c, c + num_ctas, ... does not collect the
+// heaviest tile of every round.  `entries` gets (row, relative position, 0, 0) per new token.
+extern "C" int va_plan_prefill_tiles(const int32_t* segments, int32_t num_segments, const int32_t* requests,
+                                     int32_t num_requests, int32_t per_tile, int32_t num_kv_heads,
+                                     int32_t max_ctas, int32_t* entries, int32_t num_rows, int32_t* tiles,
+                                     int32_t tile_capacity, int32_t* num_tiles_out) {
+  if (num_tiles_out == nullptr || segments == nullptr || requests == nullptr || entries == nullptr ||
+      tiles == nullptr || num_requests < 0 || num_segments < 0 || per_tile <= 0 || num_kv_heads <= 0 ||
+      max_ctas <= 0 || num_rows < 0 || tile_capacity < 0)
+    return VA_ERR_BAD_ARG;
+  struct Row {
+    int64_t cost;
+    int32_t entry_begin, entry_count, seg_begin, seg_count, head;
+  };
+  std::vector<Row> rows;
+  for (int r = 0; r < num_requests; ++r) {
+    const int32_t* rq = requests + static_cast<int64_t>(r) * 4;
+    const int seg_begin = rq[0], seg_count = rq[1], off = rq[2], S = rq[3];
+    if (seg_begin < 0 || seg_count < 0 || seg_begin + seg_count > num_segments || off < 0 || S <= 0 ||
+        off + S > num_rows)
+      return VA_ERR_BAD_ARG;
+    for (int i = 0; i < S; ++i) {
+      int32_t* e = entries + static_cast<int64_t>(off + i) * 4;
+      e[0] = off + i;
+      e[1] = i;
+      e[2] = 0;
+      e[3] = 0;
+    }
+    int64_t open_keys = 0;
+    for (int s = 0; s < seg_count; ++s) {
+      const int32_t* sg = segments + static_cast<int64_t>(seg_begin + s) * 8;
+      if (sg[4] < 0) open_keys += sg[2];
+    }
+    for (int e0 = 0; e0 < S; e0 += per_tile) {
+      const int cnt = std::min(per_tile, S - e0);
+      int64_t keys = open_keys;
+      for (int s = 0; s < seg_count; ++s) {
+        const int32_t* sg = segments + static_cast<int64_t>(seg_begin + s) * 8;
+        if (sg[4] >= 0) keys += std::min<int64_t>(sg[2], static_cast<int64_t>(sg[4]) + e0 + cnt);
+      }
+      for (int h = 0; h < num_kv_heads; ++h)
+        rows.push_back(Row{keys * cnt, off + e0, cnt, seg_begin, seg_count, h});
+    }
+  }
+  const int64_t n = static_cast<int64_t>(rows.size());
+  *num_tiles_out = static_cast<int32_t>(n);
+  if (n > tile_capacity) return VA_ERR_CAPACITY;
+  std::stable_sort(rows.begin(), rows.end(), [](const Row& a, const Row& b) { return a.cost > b.cost; });
+  const int64_t n_ctas = std::max<int64_t>(1, std::min<int64_t>(max_ctas, n));
+  for (int64_t pos = 0; pos < n; ++pos) {
+    int64_t src = pos;
+    if (n_ctas > 1) {
+      const int64_t rnd = pos / n_ctas, k = pos % n_ctas;
+      const int64_t width = std::min<int64_t>(n_ctas, n - rnd * n_ctas);   // the last round may be short
+      if (rnd & 1) src = rnd * n_ctas + (width - 1 - k);
+    }
+    const Row& t = rows[src];
+    int32_t* out = tiles + pos * 8;
+    out[0] = t.entry_begin;
+    out[1] = t.entry_count;
+    out[2] = t.seg_begin;
+    out[3] = t.seg_count;
+    out[4] = t.head;
+    out[5] = out[6] = out[7] = 0;
+  }
+  return VA_OK;
+}

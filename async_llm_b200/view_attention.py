@@ -995,43 +995,26 @@ class SharedCacheAttention:
         return meta
 
     def _upload_dense_plan(self, page_pool, segments, req_segments, n_rows, buffers=None, q_pos3=None):
-        """Tiles of tile_rows/G consecutive new tokens per (request, kv head); heaviest first."""
+        """Tiles of tile_rows/G consecutive new tokens per (request, kv head), heaviest first, every
+        other round of the CTA stride reversed: the native planner ``va_plan_prefill_tiles`` (CTA c
+        runs tiles c, c + n, ...; heaviest-first order alone hands CTA 0 the heaviest tile of every
+        round -- config 3: heaviest CTA 2.5 % above the mean instead of 6.6 %, 780 -> 805 TFLOP/s; a
+        least-loaded-CTA assignment balances better on paper (1.5 %) but measured slower (795): it
+        separates in time the tiles that share a request's K/V in L2)."""
         per_tile = self.tile_rows() // self.gqa
         seg_arr = np.asarray(segments, np.int32).reshape(-1, 8)
-        entries = np.zeros((n_rows, 4), np.int32)
+        req_arr = np.asarray(req_segments, np.int32).reshape(-1, 4)
         H = self.num_kv_heads
-        cols = []   # per request: cost, entry_begin, entry_count, seg_begin, seg_count of its row tiles
-        for seg_begin, seg_count, off, S in req_segments:
-            entries[off: off + S, 0] = np.arange(off, off + S)
-            entries[off: off + S, 1] = np.arange(S)
-            segs = seg_arr[seg_begin: seg_begin + seg_count]
-            open_keys = int(segs[segs[:, 4] < 0, 2].sum())
-            causal = segs[segs[:, 4] >= 0]
-            e0 = np.arange(0, S, per_tile, dtype=np.int64)
-            cnt = np.minimum(per_tile, S - e0)
-            # a causal segment is walked up to the last key its last row sees
-            keys = open_keys + np.minimum(causal[:, 2][None, :], causal[:, 4][None, :] + (e0 + cnt)[:, None]).sum(1)
-            n = e0.size
-            cols.append(np.stack((keys * cnt, off + e0, cnt, np.full(n, seg_begin), np.full(n, seg_count)), axis=1))
-        rows_t = np.concatenate(cols)                       # one row per (request, token tile)
-        per_head = np.repeat(rows_t, H, axis=0)             # ... and per kv head, heads adjacent
-        heads = np.tile(np.arange(H, dtype=np.int64), rows_t.shape[0])
-        order = np.argsort(-per_head[:, 0], kind="stable")  # heaviest first, ties in request order
-        # CTA c runs tiles c, c + n, c + 2n, ... (n = CTAs of the launch).  Heaviest-first order alone
-        # hands CTA 0 the heaviest tile of every round; reversing every other round evens the sums
-        # out (config 3: heaviest CTA 2.5 % above the mean instead of 6.6 %; 780 -> 805 TFLOP/s).  A
-        # least-loaded-CTA assignment with padding rows balances better on paper (1.5 %) but
-        # measured slower (795): it separates in time the tiles that share a request's K/V in L2.
-        n_tiles = order.size
-        n_ctas = self._dense_ctas(n_tiles if buffers is None else buffers.cap_tiles)
-        if n_ctas > 1:
-            pos = np.arange(n_tiles)
-            rnd, k = pos // n_ctas, pos % n_ctas
-            width = np.minimum(n_ctas, n_tiles - rnd * n_ctas)     # the last round may be short
-            order = order[np.where(rnd % 2 == 1, rnd * n_ctas + (width - 1 - k), pos)]
-        tile_arr = np.zeros((n_tiles, 8), np.int32)
-        tile_arr[:, 0:4] = per_head[order, 1:5]
-        tile_arr[:, 4] = heads[order]
+        cap = int(sum(-(-int(S) // per_tile) for _, _, _, S in req_segments)) * H
+        entries = np.empty((n_rows, 4), np.int32)
+        tile_arr = np.empty((max(cap, 1), 8), np.int32)
+        n_ctas = self._dense_ctas(cap if buffers is None else buffers.cap_tiles)
+        n_tiles = C.c_int32(0)
+        rc = _lib.lib().va_plan_prefill_tiles(seg_arr.ctypes.data, seg_arr.shape[0], req_arr.ctypes.data,
+                                              req_arr.shape[0], per_tile, H, n_ctas, entries.ctypes.data, n_rows,
+                                              tile_arr.ctypes.data, cap, C.byref(n_tiles))
+        _lib.check(rc, "va_plan_prefill_tiles")
+        tile_arr = tile_arr[: n_tiles.value]
         pages = np.asarray(page_pool, np.int32)
         if buffers is not None:
             return buffers.load(pages, tile_arr, entries, seg_arr, n_rows, q_pos3=q_pos3)

@@ -436,6 +436,20 @@ typedef struct VaViewSubs {
 int va_plan_views(const VaPlanParams* params, const VaViewStep* step, int32_t* blob, int64_t blob_words,
                   VaPlanLayout* layout, int32_t* sub_out, int64_t sub_stride, VaViewSubs* subs_info);
 
+/* Tile table of a batched view-conditioned prefill (host code).  Replaces the per-request tile
+ * bookkeeping of SharedCacheAttention.prepare_prefill_batch (shared_cache/attention.py:450-622 builds
+ * one FlashInfer plan per context depth instead).  `requests` holds (seg_begin, seg_count,
+ * row_offset, num_new) per request, `segments` the 8-word segment rows of VaDensePlan.  Writes
+ * `entries` ([num_rows, 4]: row, relative position) and `tiles` ([*num_tiles_out, 8]: entry_begin,
+ * entry_count, seg_begin, seg_count, kv head): tiles of per_tile consecutive new tokens per
+ * (request, kv head), heaviest first (keys walked x rows; stable), every other round of
+ * min(max_ctas, tiles) rows reversed.  VA_ERR_CAPACITY (with *num_tiles_out set) if tile_capacity is
+ * too small. */
+int va_plan_prefill_tiles(const int32_t* segments, int32_t num_segments, const int32_t* requests,
+                          int32_t num_requests, int32_t per_tile, int32_t num_kv_heads, int32_t max_ctas,
+                          int32_t* entries, int32_t num_rows, int32_t* tiles, int32_t tile_capacity,
+                          int32_t* num_tiles_out);
+
 /* 8. Block merge / append ------------------------------------------------------------------------
  * Replaces: SharedCacheSession._copy_slots + _shift_keys_ (shared_cache/session.py:489-528), which
  * loop over the layers in Python (index_select / index_copy_ per layer for K and V, then

@@ -177,3 +177,41 @@ def plan_decode(sub_w, sub_loc, sub_len, sub_poff, sub_tok0, sub_key, W, H, n_sm
             "entries": entries, "segments": segments, "num_partials": int(base[-1]),
             "dense_sms": dense_sms if tiles.shape[0] else 0, "num_lanes": G,
             "quota": int(work["quota"][0]), "total_keys": int(work["total_keys"][0])}
+
+
+def prefill_tiles(seg_arr, req_segments, per_tile, H, n_ctas_cap):
+    """numpy restatement of ``va_plan_prefill_tiles``: ``(entries [n_rows, 4], tiles [n, 8])``.
+
+    ``req_segments`` rows are (seg_begin, seg_count, row offset, S); a tile is ``per_tile`` consecutive
+    new tokens of one (request, kv head); heaviest first (keys walked x rows, stable), every other round
+    of ``min(n_ctas_cap, tiles)`` rows reversed."""
+    seg_arr = np.asarray(seg_arr, np.int64).reshape(-1, 8)
+    n_rows = max((off + S for _, _, off, S in req_segments), default=0)
+    entries = np.zeros((n_rows, 4), np.int32)
+    cols = []
+    for seg_begin, seg_count, off, S in req_segments:
+        entries[off: off + S, 0] = np.arange(off, off + S)
+        entries[off: off + S, 1] = np.arange(S)
+        segs = seg_arr[seg_begin: seg_begin + seg_count]
+        open_keys = int(segs[segs[:, 4] < 0, 2].sum())
+        causal = segs[segs[:, 4] >= 0]
+        e0 = np.arange(0, S, per_tile, dtype=np.int64)
+        cnt = np.minimum(per_tile, S - e0)
+        keys = open_keys + np.minimum(causal[:, 2][None, :], causal[:, 4][None, :] + (e0 + cnt)[:, None]).sum(1)
+        n = e0.size
+        cols.append(np.stack((keys * cnt, off + e0, cnt, np.full(n, seg_begin), np.full(n, seg_count)), axis=1))
+    rows_t = np.concatenate(cols)
+    per_head = np.repeat(rows_t, H, axis=0)
+    heads = np.tile(np.arange(H, dtype=np.int64), rows_t.shape[0])
+    order = np.argsort(-per_head[:, 0], kind="stable")
+    n_tiles = order.size
+    n_ctas = max(1, min(n_ctas_cap, n_tiles))
+    if n_ctas > 1:
+        pos = np.arange(n_tiles)
+        rnd, k = pos // n_ctas, pos % n_ctas
+        width = np.minimum(n_ctas, n_tiles - rnd * n_ctas)
+        order = order[np.where(rnd % 2 == 1, rnd * n_ctas + (width - 1 - k), pos)]
+    tiles = np.zeros((n_tiles, 8), np.int32)
+    tiles[:, 0:4] = per_head[order, 1:5]
+    tiles[:, 4] = heads[order]
+    return entries, tiles

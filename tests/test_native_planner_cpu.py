@@ -165,3 +165,43 @@ def test_view_entry_point_checks_its_arguments():
     view_start[0] = 0
     p.num_workers = 3
     assert call() == -1                                    # params and step disagree on the worker count
+
+
+def test_native_prefill_tile_planner_matches_the_numpy_restatement():
+    import ctypes as C
+
+    rng = np.random.default_rng(11)
+    lib = _lib.lib()
+    for case in range(40):
+        R = int(rng.integers(1, 9))
+        per_tile = int(rng.choice([4, 8, 32, 64]))
+        H = int(rng.choice([1, 2, 8]))
+        n_ctas_cap = int(rng.choice([1, 3, 16, 148]))
+        segments, reqs = [], []
+        off = 0
+        for r in range(R):
+            S = int(rng.integers(1, 300))
+            T = int(rng.integers(0, 50))
+            seg_begin = len(segments)
+            for _ in range(int(rng.integers(0, 4))):
+                segments.append([int(rng.integers(0, 99)), 0, int(rng.integers(1, 5000)), int(rng.integers(0, 9000)), -1, 0, 0, 0])
+            segments.append([int(rng.integers(0, 99)), 0, T + S, T, T, 0, 0, 0])
+            reqs.append((seg_begin, len(segments) - seg_begin, off, S))
+            off += S
+        want_entries, want_tiles = plan_numpy.prefill_tiles(segments, reqs, per_tile, H, n_ctas_cap)
+        seg_arr = np.asarray(segments, np.int32).reshape(-1, 8)
+        req_arr = np.asarray(reqs, np.int32).reshape(-1, 4)
+        cap = sum(-(-S // per_tile) for _, _, _, S in reqs) * H
+        entries = np.full((off, 4), -7, np.int32)
+        tiles = np.full((cap, 8), -7, np.int32)
+        n = C.c_int32(0)
+        rc = lib.va_plan_prefill_tiles(seg_arr.ctypes.data, seg_arr.shape[0], req_arr.ctypes.data, R, per_tile, H,
+                                       n_ctas_cap, entries.ctypes.data, off, tiles.ctypes.data, cap, C.byref(n))
+        assert rc == 0 and n.value == want_tiles.shape[0] == cap, case
+        assert np.array_equal(entries, want_entries), case
+        assert np.array_equal(tiles, want_tiles), case
+        # too small a table is refused and says how many rows it needs
+        if cap > 1:
+            rc = lib.va_plan_prefill_tiles(seg_arr.ctypes.data, seg_arr.shape[0], req_arr.ctypes.data, R, per_tile, H,
+                                           n_ctas_cap, entries.ctypes.data, off, tiles.ctypes.data, cap - 1, C.byref(n))
+            assert rc == _lib.VA_ERR_CAPACITY and n.value == cap
