@@ -627,20 +627,25 @@ __device__ __forceinline__ void frag_b_kn(uint32_t (&b)[4], uint32_t base, int l
 // stays in the accumulator registers of its sixteen warps for the whole block (a 16 x 64 tile each)
 // and is rounded to bf16 into shared memory once per chunk as the B operand of W X and Q X.
 struct PreSmem {
+  // 72.75 KB, so that three CTAs (12 warps) share an SM.  Regions are reused as the phases go:
+  //   Q tile  -> L (fp32)          once Q K^T has been taken (a CTA-wide barrier in between)
+  //   L + scratch of the inverse -> T diag(beta) and T diag(beta e^gc) (bf16) once T is complete
   static constexpr int kKs = 0;
-  static constexpr int kQs = kKs + kC * kLdD * 2;
-  static constexpr int kVs = kQs + kC * kLdD * 2;
-  static constexpr int kTb = kVs + kC * kLdD * 2;
+  static constexpr int kVs = kKs + kC * kLdD * 2;
+  static constexpr int kT = kVs + kC * kLdD * 2;
+  static constexpr int kQs = kT + kC * kLdF * 4;
+  static constexpr int kL = kQs;
+  static constexpr int kScr = kQs + kC * kLdD * 2;          // 4 x 16 x 17 fp32 of the block inverse
+  static constexpr int kTb = kQs;
   static constexpr int kTw = kTb + kC * kLdC * 2;
-  static constexpr int kL = kTw + kC * kLdC * 2;
-  static constexpr int kT = kL + kC * kLdF * 4;
-  static constexpr int kScr = kT + kC * kLdF * 4;          // 4 x 16 x 17 fp32 of the block inverse
   static constexpr int kVec = kScr + 4 * 16 * 17 * 4;
   static constexpr int kTotal = kVec + 5 * kC * 4;
+  static_assert(kC * kLdF * 4 <= kC * kLdD * 2, "L fits in the Q tile");
+  static_assert(kTw + kC * kLdC * 2 <= kVec, "T diag(beta) tiles fit in L + scratch");
 };
 
 // grid (chunk, Hv, R), 128 threads
-__global__ void __launch_bounds__(128, 2) gdn_chunk_pre_kernel(const __grid_constant__ ScanParams p) {
+__global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_constant__ ScanParams p) {
   extern __shared__ __align__(128) unsigned char csm[];
   using Sm = PreSmem;
   const uint32_t sb = smem_u32(csm);
@@ -669,39 +674,50 @@ __global__ void __launch_bounds__(128, 2) gdn_chunk_pre_kernel(const __grid_cons
   if (t0 >= t_end) return;
   const int64_t hN = static_cast<int64_t>(h) * p.num_tokens;
 
-  // ---- stage: warp w normalises tokens w, w+4, ...; tokens past the end are zeros
-  for (int i = warp; i < kC; i += 4) {
-    const int64_t tok = static_cast<int64_t>(t0) + i;
-    uint2 kn2 = make_uint2(0u, 0u), qn2 = make_uint2(0u, 0u), vraw = make_uint2(0u, 0u);
-    float bi = 0.f, gi = 0.f;
-    if (tok < t_end) {
-      const int64_t qk_off = (tok * p.num_k_heads + hk) * kD + lane * 4;
-      const uint2 kraw = *reinterpret_cast<const uint2*>(p.k + qk_off);
-      const uint2 qraw = *reinterpret_cast<const uint2*>(p.q + qk_off);
-      const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kraw);
-      const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&qraw);
-      const float2 k01 = __bfloat1622float2(kp[0]), k23 = __bfloat1622float2(kp[1]);
-      const float2 q01 = __bfloat1622float2(qp[0]), q23 = __bfloat1622float2(qp[1]);
-      const float sk = warp_sum(k01.x * k01.x + k01.y * k01.y + k23.x * k23.x + k23.y * k23.y);
-      const float sq = warp_sum(q01.x * q01.x + q01.y * q01.y + q23.x * q23.x + q23.y * q23.y);
-      const float rk = rsqrtf(sk + p.l2_eps);
-      const float rq = rsqrtf(sq + p.l2_eps) * p.q_scale;
-      kn2.x = pack_bf16(k01.x * rk, k01.y * rk);
-      kn2.y = pack_bf16(k23.x * rk, k23.y * rk);
-      qn2.x = pack_bf16(q01.x * rq, q01.y * rq);
-      qn2.y = pack_bf16(q23.x * rq, q23.y * rq);
-      vraw = *reinterpret_cast<const uint2*>(p.v + (tok * p.num_v_heads + h) * kD + lane * 4);
-      bi = p.beta[tok * p.num_v_heads + h];
-      gi = p.g[tok * p.num_v_heads + h];
-      *reinterpret_cast<uint2*>(p.s_k + (hN + tok) * kD + lane * 4) = kn2;
-      *reinterpret_cast<uint2*>(p.s_q + (hN + tok) * kD + lane * 4) = qn2;
+  // ---- stage: warp w normalises tokens w, w+4, ...; tokens past the end are zeros.  All of a warp's
+  //      16 token rows are fetched before the first is reduced (one memory latency, not sixteen).
+  {
+    uint2 kraw[kC / 4], qraw[kC / 4], vraw[kC / 4];
+#pragma unroll
+    for (int u = 0; u < kC / 4; ++u) {
+      const int64_t tok = static_cast<int64_t>(t0) + warp + 4 * u;
+      kraw[u] = qraw[u] = vraw[u] = make_uint2(0u, 0u);
+      if (tok < t_end) {
+        const int64_t qk_off = (tok * p.num_k_heads + hk) * kD + lane * 4;
+        kraw[u] = *reinterpret_cast<const uint2*>(p.k + qk_off);
+        qraw[u] = *reinterpret_cast<const uint2*>(p.q + qk_off);
+        vraw[u] = *reinterpret_cast<const uint2*>(p.v + (tok * p.num_v_heads + h) * kD + lane * 4);
+      }
     }
-    *reinterpret_cast<uint2*>(Ks + i * kLdD + lane * 4) = kn2;
-    *reinterpret_cast<uint2*>(Qs + i * kLdD + lane * 4) = qn2;
-    *reinterpret_cast<uint2*>(Vs + i * kLdD + lane * 4) = vraw;
-    if (lane == 0) {
-      be[i] = bi;
-      gg[i] = gi;
+    if (tid < kC) {
+      const int64_t tok = static_cast<int64_t>(t0) + tid;
+      be[tid] = tok < t_end ? p.beta[tok * p.num_v_heads + h] : 0.f;
+      gg[tid] = tok < t_end ? p.g[tok * p.num_v_heads + h] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < kC / 4; ++u) {
+      const int i = warp + 4 * u;
+      const int64_t tok = static_cast<int64_t>(t0) + i;
+      uint2 kn2 = make_uint2(0u, 0u), qn2 = make_uint2(0u, 0u);
+      if (tok < t_end) {
+        const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kraw[u]);
+        const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&qraw[u]);
+        const float2 k01 = __bfloat1622float2(kp[0]), k23 = __bfloat1622float2(kp[1]);
+        const float2 q01 = __bfloat1622float2(qp[0]), q23 = __bfloat1622float2(qp[1]);
+        const float sk = warp_sum(k01.x * k01.x + k01.y * k01.y + k23.x * k23.x + k23.y * k23.y);
+        const float sq = warp_sum(q01.x * q01.x + q01.y * q01.y + q23.x * q23.x + q23.y * q23.y);
+        const float rk = rsqrtf(sk + p.l2_eps);
+        const float rq = rsqrtf(sq + p.l2_eps) * p.q_scale;
+        kn2.x = pack_bf16(k01.x * rk, k01.y * rk);
+        kn2.y = pack_bf16(k23.x * rk, k23.y * rk);
+        qn2.x = pack_bf16(q01.x * rq, q01.y * rq);
+        qn2.y = pack_bf16(q23.x * rq, q23.y * rq);
+        *reinterpret_cast<uint2*>(p.s_k + (hN + tok) * kD + lane * 4) = kn2;
+        *reinterpret_cast<uint2*>(p.s_q + (hN + tok) * kD + lane * 4) = qn2;
+      }
+      *reinterpret_cast<uint2*>(Ks + i * kLdD + lane * 4) = kn2;
+      *reinterpret_cast<uint2*>(Qs + i * kLdD + lane * 4) = qn2;
+      *reinterpret_cast<uint2*>(Vs + i * kLdD + lane * 4) = vraw[u];
     }
   }
   __syncthreads();
@@ -756,6 +772,7 @@ __global__ void __launch_bounds__(128, 2) gdn_chunk_pre_kernel(const __grid_cons
         mma_bf16_16816(qk[2 * np + 1], aq, b1);
       }
     }
+    __syncthreads();   // every warp has taken its Q rows: L is written over the Q tile
     const int i0 = 16 * warp + g;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
