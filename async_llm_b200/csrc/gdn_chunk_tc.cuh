@@ -5,11 +5,15 @@
 // CTA, chunks of 64 tokens in order, operands parked by gdn_chunk_pre_kernel), but the products run
 // TRANSPOSED so that the 128 feature rows are the M dimension and the state never leaves TMEM:
 //     Xt     = X^T [dv x dk], fp32, 128 TMEM lanes x 128 columns (a summary's own layout)
-//     D1     = Xt (-W)^T                [dv x 64]   A = Xt as bf16 in shared memory, B = -W tile (K-major)
+//     D1     = Xt (-W)^T                [dv x 64]   A = a bf16 copy of Xt IN TMEM, B = -W tile (K-major)
 //     Vnew^T = U^T + D1                 by the state threads (thread = TMEM lane = dv row), written back
 //                                        to TMEM as bf16 pairs: Vnew^T and Vnew^T diag(e^(gc_last-gc))
 //     D2a    = Xt Q^T,  D2b = Vnew^T P^T   [dv x 64]   (part 0)   O^T = D2a diag(e^gc) + D2b
 //     Xt    <- e^gc_last Xt + (Vnew^T diag) K     A from TMEM, B = K tile (MN-major), accumulated in place
+// Every A operand comes from TMEM: shared memory only carries the B tiles and U.  (With the bf16 copy
+// of Xt in shared memory -- 32 KB written per chunk with four-way bank conflicts, 64 KB read by the two
+// products that use it -- two CTAs per SM ran 2.2x slower each: shared-memory bandwidth, not latency,
+// was the limit of a chunk.)
 // Per chunk the state threads read Xt once (bf16 copy for the next products, scaled fp32 back), the
 // MMA warp issues 24 (part 0) or 12 products from one elected lane, loader warps fetch the next
 // chunk's tiles into the other buffer.  mma.sync cannot do better here: the previous kernel ran at
@@ -19,9 +23,22 @@
 // loops, TMEM is freed and the kernel returns (the status word of ScanParams is optional).
 // (gdn.cu includes tc05.cuh at file scope before this file.)
 
+#ifdef GDN_TC_PROF
+__device__ unsigned long long g_tc_prof[16][64];   // [event][chunk] globaltimer ns, CTA (0,0,0)
+__device__ __forceinline__ void tc_prof(int ev, int c, bool who) {
+  if (who && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && c < 64) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_tc_prof[ev][c] = t;
+  }
+}
+#define TC_PROF(ev, c, who) tc_prof(ev, c, who)
+#else
+#define TC_PROF(ev, c, who)
+#endif
+
 struct TcStateSmem {
-  static constexpr int kXt = 0;                        // Xt bf16 [128][128], swizzled, 32 KB
-  static constexpr int kBuf = kXt + 128 * 128 * 2;     // two buffers of the chunk's tiles
+  static constexpr int kBuf = 0;                       // two buffers of the chunk's tiles
   static constexpr int kW = 0;                         // -W [64][128] swizzled (B, K-major)
   static constexpr int kK = kW + kC * kD * 2;          // K  [64][128] swizzled (B, MN-major)
   static constexpr int kQ = kK + kC * kD * 2;          // Q  [64][128] swizzled (B, K-major)    part 0
@@ -29,7 +46,9 @@ struct TcStateSmem {
   static constexpr int kU = kP + kC * kC * 2;          // U  [64][128] plain rows (read by the state threads)
   static constexpr int kVec = kU + kC * kD * 2;        // e^gc [64], e^(gc_last-gc) [64] fp32
   static constexpr int kBufBytes = ((kVec + 2 * kC * 4 + 1023) / 1024) * 1024;
-  static constexpr int kBar = kBuf + 2 * kBufBytes;
+  static constexpr int kOut = kBuf + 2 * kBufBytes;    // 4 warps x [64 tokens][32 dv] bf16 (+16 B per row): output staging
+  static constexpr int kOutRow = 32 * 2 + 16;
+  static constexpr int kBar = kOut + 4 * kC * kOutRow;
   static constexpr int kTotal = kBar + 256;
   static_assert(kTotal <= 227 * 1024, "shared memory of the tcgen05 chunk state kernel");
 };
@@ -37,10 +56,10 @@ struct TcStateSmem {
 enum TcStateBar : int { kSbFull = 0, kSbEmpty = 2, kSbXsReady = 4, kSbD1Done = 5, kSbAReady = 6, kSbMmaDone = 7, kSbCount = 8 };
 constexpr int kTcStateThreads = 256;   // warps 0-3 state (TMEM lanes), 4 MMA, 5-7 loaders
 constexpr int kTcStatePolls = 1 << 18;
-// TMEM columns (384 used of the 512 allocated): Xt, D1, the two output accumulators, the A operands.
-// (Alternating pairs of output accumulators, written out while the next chunk's first product runs,
-// were measured and were not faster.)
-constexpr int kColXt = 0, kColD1 = 128, kColD2a = 192, kColD2b = 256, kColA1 = 320, kColA2 = 352;
+// TMEM columns (448 used of the 512 allocated): Xt fp32, its bf16 copy (A operand), D1, the two output
+// accumulators, the two A operands made from Vnew^T.  (Alternating pairs of output accumulators,
+// written out while the next chunk's first product runs, were measured and were not faster.)
+constexpr int kColXt = 0, kColXtB = 128, kColD1 = 192, kColD2a = 256, kColD2b = 320, kColA1 = 384, kColA2 = 416;
 
 __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(const __grid_constant__ ScanParams p) {
   using Sm = TcStateSmem;
@@ -88,7 +107,7 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
     if (dead) return false;
     const uint32_t b = bar(slot);
     for (int i = 0; i < kTcStatePolls; ++i) {
-      if (mbar_try_wait_hint(b, parity & 1u, 1000)) return true;
+      if (mbar_try_wait(b, parity & 1u)) return true;   // (a suspend-time hint, or spinning on test_wait, were both slower)
       if ((i & 63) == 63 && *abort_flag != 0) break;
     }
     dead = true;
@@ -151,13 +170,13 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
     const uint32_t elected = elect_one();
     const uint32_t idesc_n64 = instr_desc(kC, false);
     const uint32_t idesc_n128 = instr_desc(kD, true);
-    const uint64_t xt_desc = smem_desc(sb + Sm::kXt, 16, 1024);
     for (int c = 0; c < n_chunks; ++c) {
       const int b = c & 1;
       const uint32_t base = sb + Sm::kBuf + b * Sm::kBufBytes;
       if (!wait_warp(kSbFull + b, (c >> 1) & 1u)) break;
       if (!wait_warp(kSbXsReady, c & 1u)) break;
       tc_fence_after();
+      TC_PROF(0, c, lane == 0);
       const uint64_t w_desc = smem_desc(base + Sm::kW, 16, 1024);
       const uint64_t q_desc = smem_desc(base + Sm::kQ, 16, 1024);
       const uint64_t p_desc = smem_desc(base + Sm::kP, 16, 1024);
@@ -165,17 +184,19 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       // D1 = Xt (-W)^T : panel ks / 4, 32 bytes per step inside it
 #pragma unroll
       for (int ks = 0; ks < kD / 16; ++ks)
-        umma(elected, tmem_base + kColD1, xt_desc + static_cast<uint64_t>((ks >> 2) * (128 * 8) + (ks & 3) * 2),
-             w_desc + static_cast<uint64_t>((ks >> 2) * (kC * 8) + (ks & 3) * 2), idesc_n64, ks > 0);
+        umma_ts(elected, tmem_base + kColD1, tmem_base + kColXtB + ks * 8,
+                w_desc + static_cast<uint64_t>((ks >> 2) * (kC * 8) + (ks & 3) * 2), idesc_n64, ks > 0);
       umma_commit(elected, bar(kSbD1Done));
       if (part == 0) {
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks)
-          umma(elected, tmem_base + kColD2a, xt_desc + static_cast<uint64_t>((ks >> 2) * (128 * 8) + (ks & 3) * 2),
-               q_desc + static_cast<uint64_t>((ks >> 2) * (kC * 8) + (ks & 3) * 2), idesc_n64, ks > 0);
+          umma_ts(elected, tmem_base + kColD2a, tmem_base + kColXtB + ks * 8,
+                  q_desc + static_cast<uint64_t>((ks >> 2) * (kC * 8) + (ks & 3) * 2), idesc_n64, ks > 0);
       }
+      TC_PROF(1, c, lane == 0);
       if (!wait_warp(kSbAReady, c & 1u)) break;
       tc_fence_after();
+      TC_PROF(2, c, lane == 0);
       if (part == 0) {
 #pragma unroll
         for (int ks = 0; ks < kC / 16; ++ks)
@@ -188,6 +209,7 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
                 idesc_n128, true);
       umma_commit(elected, bar(kSbMmaDone));
       umma_commit(elected, bar(kSbEmpty + b));
+      TC_PROF(3, c, lane == 0);
     }
     dead = __any_sync(0xffffffffu, dead);
   } else {
@@ -222,20 +244,43 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       }
       tc_fence_before();
     }
-    // O^T of the chunk at t0 from D2a, D2b (part 0)
-    auto write_out = [&](int t0, const float* eg) {
+    // O^T of a chunk (part 0): read out of TMEM as soon as its products are done (bf16 pairs of
+    // tokens 2i, 2i+1 of this thread's dv row), written to global memory later, off the chunk's
+    // critical chain, through a per-warp staging tile so that the global stores are 16 bytes wide
+    uint32_t o_pk[kC / 2];
+    auto read_out = [&](const float* eg) {
 #pragma unroll
       for (int q0 = 0; q0 < kC; q0 += 32) {
         float a[32], bq[32];
         tmem_ld32(lane_addr + kColD2a + q0, a);
         tmem_ld32(lane_addr + kColD2b + q0, bq);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int tok = t0 + q0 + i;
-          if (tok < t_end)
-            p.out[(static_cast<int64_t>(tok) * p.num_v_heads + h) * kD + L] = __float2bfloat16_rn(fmaf(a[i], eg[q0 + i], bq[i]));
+        for (int i = 0; i < 32; i += 2)
+          o_pk[(q0 + i) >> 1] = pack_bf16(fmaf(a[i], eg[q0 + i], bq[i]), fmaf(a[i + 1], eg[q0 + i + 1], bq[i + 1]));
+      }
+    };
+    auto store_out = [&](int t0) {
+      unsigned char* stage = tsm + Sm::kOut + warp * (kC * Sm::kOutRow);
+#pragma unroll
+      for (int i = 0; i < kC / 2; ++i) {
+        *reinterpret_cast<__nv_bfloat16*>(stage + (2 * i) * Sm::kOutRow + lane * 2) =
+            __ushort_as_bfloat16(static_cast<unsigned short>(o_pk[i] & 0xffffu));
+        *reinterpret_cast<__nv_bfloat16*>(stage + (2 * i + 1) * Sm::kOutRow + lane * 2) =
+            __ushort_as_bfloat16(static_cast<unsigned short>(o_pk[i] >> 16));
+      }
+      __syncwarp();
+      // 64 tokens x 64 bytes of this warp's 32 dv columns: 4 lanes per token, 8 tokens per pass
+#pragma unroll
+      for (int pass = 0; pass < kC / 8; ++pass) {
+        const int j = pass * 8 + (lane >> 2);
+        const int piece = lane & 3;
+        const int tok = t0 + j;
+        if (tok < t_end) {
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + j * Sm::kOutRow + piece * 16);
+          *reinterpret_cast<uint4*>(p.out + (static_cast<int64_t>(tok) * p.num_v_heads + h) * kD + warp * 32 + piece * 8) = v;
         }
       }
+      __syncwarp();
     };
     for (int c = 0; c < n_chunks && !dead; ++c) {
       const int b = c & 1;
@@ -243,35 +288,31 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       unsigned char* bufp = tsm + Sm::kBuf + b * Sm::kBufBytes;
       const float* eg = reinterpret_cast<const float*>(bufp + Sm::kVec);
       const float* ed = eg + kC;
+      TC_PROF(4, c, tid == 0);
       if (!wait_warp(kSbFull + b, (c >> 1) & 1u)) break;
+      TC_PROF(5, c, tid == 0);
       if (c > 0) {
         if (!wait_warp(kSbMmaDone, (c - 1) & 1u)) break;
         tc_fence_after();
-        if (part == 0) {
-          const float* eg_prev = reinterpret_cast<const float*>(tsm + Sm::kBuf + (b ^ 1) * Sm::kBufBytes + Sm::kVec);
-          write_out(t0 - kC, eg_prev);
-        }
+        TC_PROF(6, c, tid == 0);
+        if (part == 0) read_out(reinterpret_cast<const float*>(tsm + Sm::kBuf + (b ^ 1) * Sm::kBufBytes + Sm::kVec));
         // the previous chunk's buffer is no longer read by these threads
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kSbEmpty + (b ^ 1)));
       }
-      // ---- Xt: bf16 copy into shared memory (A operand of the next products), fp32 scaled by the
-      //      chunk's total decay back into TMEM (the state update accumulates on top of it)
+      TC_PROF(7, c, tid == 0);
+      // ---- Xt: bf16 copy into TMEM (A operand of the next products), fp32 scaled by the chunk's
+      //      total decay back in place (the state update accumulates on top of it)
       const int n_live = min(kC, t_end - t0);
       const float tail = eg[n_live - 1];   // tokens past the end do not decay the state
 #pragma unroll
       for (int q0 = 0; q0 < kD; q0 += 32) {
         float v[32];
         tmem_ld32(lane_addr + kColXt + q0, v);
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 pk;
-          pk.x = pack_bf16(v[i], v[i + 1]);
-          pk.y = pack_bf16(v[i + 2], v[i + 3]);
-          pk.z = pack_bf16(v[i + 4], v[i + 5]);
-          pk.w = pack_bf16(v[i + 6], v[i + 7]);
-          *reinterpret_cast<uint4*>(tsm + Sm::kXt + sw_off(L, (q0 + i) >> 3, 128)) = pk;
-        }
+        for (int i = 0; i < 32; i += 2) pk[i >> 1] = pack_bf16(v[i], v[i + 1]);
+        tmem_st16_issue(lane_addr + kColXtB + (q0 >> 1), pk);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= tail;
         tmem_st32(lane_addr + kColXt + q0, v);
@@ -280,9 +321,12 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kSbXsReady));
+      TC_PROF(8, c, tid == 0);
+      if (c > 0 && part == 0) store_out(t0 - kC);   // while the tensor core works on D1
       // ---- Vnew^T = U^T + D1 ; bf16 pairs of it and of its decayed form into TMEM (A operands)
       if (!wait_warp(kSbD1Done, c & 1u)) break;
       tc_fence_after();
+      TC_PROF(9, c, tid == 0);
       const __nv_bfloat16* Us = reinterpret_cast<const __nv_bfloat16*>(bufp + Sm::kU);
 #pragma unroll
       for (int q0 = 0; q0 < kC; q0 += 32) {
@@ -305,6 +349,7 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kSbAReady));
+      TC_PROF(10, c, tid == 0);
     }
     // ---- the last chunk's output rows, then the state
     if (!dead && n_chunks > 0) {
@@ -312,7 +357,10 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       if (wait_warp(kSbMmaDone, c & 1u)) {
         tc_fence_after();
         if (part == 0)
-          write_out(t_begin + c * kC, reinterpret_cast<const float*>(tsm + Sm::kBuf + (c & 1) * Sm::kBufBytes + Sm::kVec));
+        {
+          read_out(reinterpret_cast<const float*>(tsm + Sm::kBuf + (c & 1) * Sm::kBufBytes + Sm::kVec));
+          store_out(t_begin + c * kC);
+        }
       }
     }
     if (!dead) {
