@@ -1195,12 +1195,6 @@ int check_gdn_dims(int num_k_heads, int num_v_heads, int dk, int dv) {
 
 }  // namespace
 
-#ifdef GDN_TC_PROF
-extern "C" int va_debug_gdn_tc_prof(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(g_tc_prof)) == cudaSuccess ? 0 : -1;
-}
-#endif
-
 extern "C" int va_gdn_step(const VaGdnStep* a, va_stream_t stream) {
   if (a == nullptr) return VA_ERR_BAD_ARG;
   int rc = check_gdn_dims(a->num_k_heads, a->num_v_heads, a->head_k_dim, a->head_v_dim);

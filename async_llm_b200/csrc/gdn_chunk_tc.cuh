@@ -23,20 +23,6 @@
 // loops, TMEM is freed and the kernel returns (the status word of ScanParams is optional).
 // (gdn.cu includes tc05.cuh at file scope before this file.)
 
-#ifdef GDN_TC_PROF
-__device__ unsigned long long g_tc_prof[16][64];   // [event][chunk] globaltimer ns, CTA (0,0,0)
-__device__ __forceinline__ void tc_prof(int ev, int c, bool who) {
-  if (who && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && c < 64) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    g_tc_prof[ev][c] = t;
-  }
-}
-#define TC_PROF(ev, c, who) tc_prof(ev, c, who)
-#else
-#define TC_PROF(ev, c, who)
-#endif
-
 struct TcStateSmem {
   static constexpr int kBuf = 0;                       // two buffers of the chunk's tiles
   static constexpr int kW = 0;                         // -W [64][128] swizzled (B, K-major)
@@ -176,7 +162,6 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       if (!wait_warp(kSbFull + b, (c >> 1) & 1u)) break;
       if (!wait_warp(kSbXsReady, c & 1u)) break;
       tc_fence_after();
-      TC_PROF(0, c, lane == 0);
       const uint64_t w_desc = smem_desc(base + Sm::kW, 16, 1024);
       const uint64_t q_desc = smem_desc(base + Sm::kQ, 16, 1024);
       const uint64_t p_desc = smem_desc(base + Sm::kP, 16, 1024);
@@ -193,10 +178,8 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
           umma_ts(elected, tmem_base + kColD2a, tmem_base + kColXtB + ks * 8,
                   q_desc + static_cast<uint64_t>((ks >> 2) * (kC * 8) + (ks & 3) * 2), idesc_n64, ks > 0);
       }
-      TC_PROF(1, c, lane == 0);
       if (!wait_warp(kSbAReady, c & 1u)) break;
       tc_fence_after();
-      TC_PROF(2, c, lane == 0);
       if (part == 0) {
 #pragma unroll
         for (int ks = 0; ks < kC / 16; ++ks)
@@ -209,7 +192,6 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
                 idesc_n128, true);
       umma_commit(elected, bar(kSbMmaDone));
       umma_commit(elected, bar(kSbEmpty + b));
-      TC_PROF(3, c, lane == 0);
     }
     dead = __any_sync(0xffffffffu, dead);
   } else {
@@ -288,19 +270,15 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       unsigned char* bufp = tsm + Sm::kBuf + b * Sm::kBufBytes;
       const float* eg = reinterpret_cast<const float*>(bufp + Sm::kVec);
       const float* ed = eg + kC;
-      TC_PROF(4, c, tid == 0);
       if (!wait_warp(kSbFull + b, (c >> 1) & 1u)) break;
-      TC_PROF(5, c, tid == 0);
       if (c > 0) {
         if (!wait_warp(kSbMmaDone, (c - 1) & 1u)) break;
         tc_fence_after();
-        TC_PROF(6, c, tid == 0);
         if (part == 0) read_out(reinterpret_cast<const float*>(tsm + Sm::kBuf + (b ^ 1) * Sm::kBufBytes + Sm::kVec));
         // the previous chunk's buffer is no longer read by these threads
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kSbEmpty + (b ^ 1)));
       }
-      TC_PROF(7, c, tid == 0);
       // ---- Xt: bf16 copy into TMEM (A operand of the next products), fp32 scaled by the chunk's
       //      total decay back in place (the state update accumulates on top of it)
       const int n_live = min(kC, t_end - t0);
@@ -321,12 +299,10 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kSbXsReady));
-      TC_PROF(8, c, tid == 0);
       if (c > 0 && part == 0) store_out(t0 - kC);   // while the tensor core works on D1
       // ---- Vnew^T = U^T + D1 ; bf16 pairs of it and of its decayed form into TMEM (A operands)
       if (!wait_warp(kSbD1Done, c & 1u)) break;
       tc_fence_after();
-      TC_PROF(9, c, tid == 0);
       const __nv_bfloat16* Us = reinterpret_cast<const __nv_bfloat16*>(bufp + Sm::kU);
 #pragma unroll
       for (int q0 = 0; q0 < kC; q0 += 32) {
@@ -349,7 +325,6 @@ __global__ void __launch_bounds__(kTcStateThreads, 1) gdn_chunk_state_tc_kernel(
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kSbAReady));
-      TC_PROF(10, c, tid == 0);
     }
     // ---- the last chunk's output rows, then the state
     if (!dead && n_chunks > 0) {
