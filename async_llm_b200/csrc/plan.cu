@@ -167,21 +167,53 @@ extern "C" int va_plan_decode(const VaPlanParams* params, int32_t num_subs, cons
           total += sub_len[sub];
           s.uend.push_back(total);
         }
-    quota = ceil_div(total, std::max(G, 1));
-    quota = std::max<int64_t>(p.min_item_keys, ceil_div(quota, 16) * 16);
-    // every lookup below walks forward: the cuts, the unit bounds and the item begins all ascend
+    // Lane cuts that even out the lanes' TIME, not their keys.  A lane streams its keys in stages of
+    // 16 and pays about one stage more per item (query staging, the partial's write-out), so its cost
+    // is sum over its items of ceil(keys / 16) + 1.  With equal key quotas a lane that contains a unit
+    // boundary ran 1-3 stages longer than one that does not (cuts close to a boundary snap onto it):
+    // on the shared-prefix decode configuration the last lane ended 3.5 us after the median lane, now
+    // 2 us (the step gained 0.7 us: the memory system, not a lane's own pace, sets most of the time).  Here the smallest budget T
+    // (in stages) is found for which a greedy walk needs at most G lanes; an item is never shorter
+    // than cut_slack_keys unless it is a whole unit.
+    const int64_t piece_min = std::max<int64_t>(16, p.cut_slack_keys);
+    auto walk = [&](int64_t T, std::vector<int64_t>* cuts) -> int64_t {
+      int64_t lanes = 0, pos = 0, u = 0;
+      while (pos < total) {
+        ++lanes;
+        int64_t budget = T;
+        bool empty = true;
+        while (pos < total) {
+          while (s.uend[u] <= pos) ++u;
+          const int64_t rem = s.uend[u] - pos;
+          const int64_t avail = budget - 1;                 // stages left for keys once the item is paid for
+          const int64_t need = ceil_div(rem, 16);
+          if (need <= avail) {                              // the rest of the unit fits
+            pos = s.uend[u];
+            budget -= need + 1;
+            empty = false;
+            continue;
+          }
+          int64_t take = std::max<int64_t>(avail, 0) * 16;  // keys of this unit the lane can still afford
+          if (empty) {
+            take = std::max(take, std::min(piece_min, rem));        // an empty lane always advances
+            if (rem - take < piece_min) take = rem;
+          } else {
+            if (rem - take < piece_min) take = (rem - piece_min) / 16 * 16;   // leave no sliver behind
+            if (take < piece_min) take = 0;                                  // and start none
+          }
+          pos += take;
+          break;
+        }
+        if (cuts != nullptr && pos < total) cuts->push_back(pos);
+      }
+      return lanes;
+    };
+    const int64_t lanes_cap = std::max(G, 1);
+    int64_t T = std::max<int64_t>(ceil_div(ceil_div(total, 16) + n_units, lanes_cap), ceil_div(p.min_item_keys, 16) + 1);
+    while (walk(T, nullptr) > lanes_cap) ++T;
+    quota = T * 16;
     s.lane_cuts.clear();
-    int64_t iu = 0, ip = 0;
-    for (int64_t c = quota; c < total; c += quota) {
-      // a cut that would leave a sliver next to a unit boundary moves onto that boundary
-      while (iu < n_units - 1 && s.uend[iu] < c) ++iu;           // first unit that ends at or after c
-      while (ip + 1 < n_units && s.ustart[ip + 1] <= c) ++ip;    // last unit that starts at or before c
-      const int64_t nxt = s.uend[iu], prv = s.ustart[ip];
-      int64_t cut = (nxt - c < p.cut_slack_keys) ? nxt : c;
-      cut = (cut - prv < p.cut_slack_keys) ? prv : cut;
-      s.lane_cuts.push_back(cut);
-    }
-    // (the adjusted cuts stay ascending: each moves by less than cut_slack_keys < quota / 2)
+    walk(T, &s.lane_cuts);
     s.cuts.resize(s.ustart.size() + s.lane_cuts.size());
     std::merge(s.ustart.begin(), s.ustart.end(), s.lane_cuts.begin(), s.lane_cuts.end(), s.cuts.begin());
     s.cuts.push_back(total);

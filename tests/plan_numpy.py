@@ -42,15 +42,48 @@ def build_decode_work(
     ustart = uend - ulen
     total = int(uend[-1]) if n_units else 0
 
-    quota = -(-total // max(G, 1))
-    quota = max(MIN_ITEM_KEYS, -(-quota // 16) * 16)
-    lane_cuts = np.arange(quota, total, quota, dtype=np.int64)
-    if lane_cuts.size:
-        # a cut that would leave a sliver next to a unit boundary moves onto that boundary
-        nxt = uend[np.searchsorted(uend, lane_cuts, side="left").clip(max=n_units - 1)]
-        prv = ustart[np.searchsorted(ustart, lane_cuts, side="right") - 1]
-        lane_cuts = np.where(nxt - lane_cuts < CUT_SLACK_KEYS, nxt, lane_cuts)
-        lane_cuts = np.where(lane_cuts - prv < CUT_SLACK_KEYS, prv, lane_cuts)
+    # lane cuts that even out the lanes' cost = sum over items of ceil(keys / 16) + 1 stages: the
+    # smallest budget T for which a greedy walk needs at most G lanes
+    piece_min = max(16, CUT_SLACK_KEYS)
+
+    def walk(T):
+        cuts, lanes, pos, u = [], 0, 0, 0
+        while pos < total:
+            lanes += 1
+            budget, empty = T, True
+            while pos < total:
+                while uend[u] <= pos:
+                    u += 1
+                rem = int(uend[u]) - pos
+                avail = budget - 1
+                need = -(-rem // 16)
+                if need <= avail:
+                    pos = int(uend[u])
+                    budget -= need + 1
+                    empty = False
+                    continue
+                take = max(avail, 0) * 16
+                if empty:
+                    take = max(take, min(piece_min, rem))
+                    if rem - take < piece_min:
+                        take = rem
+                else:
+                    if rem - take < piece_min:
+                        take = (rem - piece_min) // 16 * 16
+                    if take < piece_min:
+                        take = 0
+                pos += take
+                break
+            if pos < total:
+                cuts.append(pos)
+        return lanes, cuts
+
+    lanes_cap = max(G, 1)
+    T = max(-(-(-(-total // 16) + n_units) // lanes_cap), -(-MIN_ITEM_KEYS // 16) + 1)
+    while walk(T)[0] > lanes_cap:
+        T += 1
+    quota = T * 16
+    lane_cuts = np.asarray(walk(T)[1], np.int64)
     cuts = np.unique(np.concatenate((ustart, lane_cuts, np.array([total], np.int64))))
     begin, end = cuts[:-1], cuts[1:]
     n_items = int(begin.shape[0])
