@@ -53,7 +53,9 @@ def test_prefill_batch_becomes_context_free_prefill_specs():
 def test_registration_in_the_host_registry():
     try:
         import sys, os
-        for path in (os.environ.get("ASYNC_LLM_REFERENCE_PYTHON"), "/root/reference/python"):
+        here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        for path in (os.environ.get("ASYNC_LLM_REFERENCE_PYTHON"),
+                     os.path.join(os.path.dirname(here), "reference", "python")):   # a checkout beside this repository
             if path and os.path.isdir(os.path.join(path, "minisgl")) and path not in sys.path:
                 sys.path.insert(0, path)
         from minisgl.attention import SUPPORTED_ATTENTION_BACKENDS, validate_attn_backend

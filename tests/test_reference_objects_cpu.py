@@ -19,7 +19,10 @@ from async_llm_b200 import PrefillSpec, SharedCacheAttention
 from async_llm_b200.view_attention import SharedDecodeAttentionBuffers
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CANDIDATES = [os.environ.get("ASYNC_LLM_REFERENCE_PYTHON"), "/root/reference/python",
+# the reference's python tree: named by the environment, a checkout beside this repository, or the
+# unmodified install under baseline/_ref
+CANDIDATES = [os.environ.get("ASYNC_LLM_REFERENCE_PYTHON"),
+              os.path.join(os.path.dirname(ROOT), "reference", "python"),
               os.path.join(ROOT, "baseline", "_ref")]
 
 
