@@ -674,50 +674,95 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
   if (t0 >= t_end) return;
   const int64_t hN = static_cast<int64_t>(h) * p.num_tokens;
 
-  // ---- stage: warp w normalises tokens w, w+4, ...; tokens past the end are zeros.  All of a warp's
-  //      16 token rows are fetched before the first is reduced (one memory latency, not sixteen).
+  // ---- stage: the raw K, Q and V rows of the chunk go straight to their shared-memory tiles as
+  //      16-byte asynchronous copies (3072 of them, 24 per thread, all in flight at once); rows past
+  //      the end are zero-filled.  (Register loads did not do: with 218 KB of the SM's 256 KB taken
+  //      as shared memory by the three resident CTAs the L1 keeps few lines for misses in flight,
+  //      and a warp's 48 row loads took 10 us.)  The rows are then normalised in place.
   {
-    uint2 kraw[kC / 4], qraw[kC / 4], vraw[kC / 4];
+    constexpr int kRowChunks = kD / 8;              // 16-byte chunks of a row
+    constexpr int kTileChunks = kC * kRowChunks;
 #pragma unroll
-    for (int u = 0; u < kC / 4; ++u) {
-      const int64_t tok = static_cast<int64_t>(t0) + warp + 4 * u;
-      kraw[u] = qraw[u] = vraw[u] = make_uint2(0u, 0u);
-      if (tok < t_end) {
-        const int64_t qk_off = (tok * p.num_k_heads + hk) * kD + lane * 4;
-        kraw[u] = *reinterpret_cast<const uint2*>(p.k + qk_off);
-        qraw[u] = *reinterpret_cast<const uint2*>(p.q + qk_off);
-        vraw[u] = *reinterpret_cast<const uint2*>(p.v + (tok * p.num_v_heads + h) * kD + lane * 4);
-      }
+    for (int j = 0; j < 3 * kTileChunks / 128; ++j) {
+      const int idx = tid + 128 * j;
+      const int which = idx / kTileChunks;          // 0 = K, 1 = Q, 2 = V (uniform per j)
+      const int rem = idx - which * kTileChunks;
+      const int i = rem / kRowChunks;
+      const int ch = rem - i * kRowChunks;
+      const int64_t tok = static_cast<int64_t>(t0) + i;
+      const bool live = tok < t_end;
+      const int64_t row = live ? tok : static_cast<int64_t>(t0);
+      const __nv_bfloat16* src = which == 2 ? p.v + (row * p.num_v_heads + h) * kD
+                                            : (which == 0 ? p.k : p.q) + (row * p.num_k_heads + hk) * kD;
+      const uint32_t dst = sb + (which == 0 ? Sm::kKs : which == 1 ? Sm::kQs : Sm::kVs) + (i * kLdD + ch * 8) * 2;
+      cp_async16(dst, src + ch * 8, live ? 16 : 0);
     }
+    cp_async_commit();
     if (tid < kC) {
       const int64_t tok = static_cast<int64_t>(t0) + tid;
       be[tid] = tok < t_end ? p.beta[tok * p.num_v_heads + h] : 0.f;
       gg[tid] = tok < t_end ? p.g[tok * p.num_v_heads + h] : 0.f;
     }
+    cp_async_wait<0>();
+    __syncthreads();
+    // eight lanes per token (lane l owns the 16-byte pieces l and l + 8 of the row), four tokens per
+    // warp at once, the CTA's 64 tokens in four passes: three shuffle steps per reduction
+    const int r4 = lane >> 3, l8 = lane & 7;
 #pragma unroll
-    for (int u = 0; u < kC / 4; ++u) {
-      const int i = warp + 4 * u;
+    for (int ps = 0; ps < kC / 16; ++ps) {
+      const int i = ps * 16 + warp * 4 + r4;
       const int64_t tok = static_cast<int64_t>(t0) + i;
-      uint2 kn2 = make_uint2(0u, 0u), qn2 = make_uint2(0u, 0u);
-      if (tok < t_end) {
-        const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kraw[u]);
-        const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&qraw[u]);
-        const float2 k01 = __bfloat1622float2(kp[0]), k23 = __bfloat1622float2(kp[1]);
-        const float2 q01 = __bfloat1622float2(qp[0]), q23 = __bfloat1622float2(qp[1]);
-        const float sk = warp_sum(k01.x * k01.x + k01.y * k01.y + k23.x * k23.x + k23.y * k23.y);
-        const float sq = warp_sum(q01.x * q01.x + q01.y * q01.y + q23.x * q23.x + q23.y * q23.y);
+      const bool live = tok < t_end;   // rows past the end are zeros and stay zeros
+      {
+        uint4 kr[2], qr[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          kr[c] = *reinterpret_cast<const uint4*>(Ks + i * kLdD + (l8 + 8 * c) * 8);
+          qr[c] = *reinterpret_cast<const uint4*>(Qs + i * kLdD + (l8 + 8 * c) * 8);
+        }
+        float kf[16], qf[16];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr[c]);
+          const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&qr[c]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 a = __bfloat1622float2(kp[e]), b = __bfloat1622float2(qp[e]);
+            kf[8 * c + 2 * e] = a.x;
+            kf[8 * c + 2 * e + 1] = a.y;
+            qf[8 * c + 2 * e] = b.x;
+            qf[8 * c + 2 * e + 1] = b.y;
+          }
+        }
+        float sk = 0.f, sq = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          sk = fmaf(kf[e], kf[e], sk);
+          sq = fmaf(qf[e], qf[e], sq);
+        }
+        sk = row_sum(sk);
+        sq = row_sum(sq);
         const float rk = rsqrtf(sk + p.l2_eps);
         const float rq = rsqrtf(sq + p.l2_eps) * p.q_scale;
-        kn2.x = pack_bf16(k01.x * rk, k01.y * rk);
-        kn2.y = pack_bf16(k23.x * rk, k23.y * rk);
-        qn2.x = pack_bf16(q01.x * rq, q01.y * rq);
-        qn2.y = pack_bf16(q23.x * rq, q23.y * rq);
-        *reinterpret_cast<uint2*>(p.s_k + (hN + tok) * kD + lane * 4) = kn2;
-        *reinterpret_cast<uint2*>(p.s_q + (hN + tok) * kD + lane * 4) = qn2;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint4 kn4, qn4;
+          kn4.x = pack_bf16(kf[8 * c] * rk, kf[8 * c + 1] * rk);
+          kn4.y = pack_bf16(kf[8 * c + 2] * rk, kf[8 * c + 3] * rk);
+          kn4.z = pack_bf16(kf[8 * c + 4] * rk, kf[8 * c + 5] * rk);
+          kn4.w = pack_bf16(kf[8 * c + 6] * rk, kf[8 * c + 7] * rk);
+          qn4.x = pack_bf16(qf[8 * c] * rq, qf[8 * c + 1] * rq);
+          qn4.y = pack_bf16(qf[8 * c + 2] * rq, qf[8 * c + 3] * rq);
+          qn4.z = pack_bf16(qf[8 * c + 4] * rq, qf[8 * c + 5] * rq);
+          qn4.w = pack_bf16(qf[8 * c + 6] * rq, qf[8 * c + 7] * rq);
+          if (live) {
+            *reinterpret_cast<uint4*>(p.s_k + (hN + tok) * kD + (l8 + 8 * c) * 8) = kn4;
+            *reinterpret_cast<uint4*>(p.s_q + (hN + tok) * kD + (l8 + 8 * c) * 8) = qn4;
+            *reinterpret_cast<uint4*>(Ks + i * kLdD + (l8 + 8 * c) * 8) = kn4;
+            *reinterpret_cast<uint4*>(Qs + i * kLdD + (l8 + 8 * c) * 8) = qn4;
+          }
+        }
       }
-      *reinterpret_cast<uint2*>(Ks + i * kLdD + lane * 4) = kn2;
-      *reinterpret_cast<uint2*>(Qs + i * kLdD + lane * 4) = qn2;
-      *reinterpret_cast<uint2*>(Vs + i * kLdD + lane * 4) = vraw[u];
     }
   }
   __syncthreads();
@@ -794,8 +839,8 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
   //   diagonal block I:  T_II = (I - L_II)^-1 by forward substitution; warp I, lane j keeps column j
   //                      in registers (T[i][j] = L[i][j] + sum_{j<m<i} L[i][m] T[m][j])
   //   block (I, J), I>J: T_IJ = T_II (sum_{M=J}^{I-1} L_IM T_MJ), by block distance I - J = 1, 2, 3
-  for (int idx = tid; idx < kC * kC; idx += 128) Tm[(idx / kC) * kLdF + idx % kC] = 0.f;
-  __syncthreads();
+  //   (blocks above the diagonal are never written or read: they are zeros by construction)
+  __syncthreads();   // L is complete
   if (lane < 16) {
     const int b0 = 16 * warp;
     float tj[16];
@@ -853,11 +898,16 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
       __syncthreads();
     }
   }
-  for (int idx = tid; idx < kC * kC; idx += 128) {
-    const int i = idx / kC, j = idx - i * kC;
-    const float tij = Tm[i * kLdF + j];
-    Tb[i * kLdC + j] = __float2bfloat16_rn(tij * be[j]);
-    Tw[i * kLdC + j] = __float2bfloat16_rn(tij * be[j] * eg[j]);
+  // T diag(beta) and T diag(beta e^gc) as bf16, two columns per thread and step
+#pragma unroll 4
+  for (int idx = tid; idx < kC * kC / 2; idx += 128) {
+    const int i = idx / (kC / 2), j = 2 * (idx - i * (kC / 2));
+    const bool upper = (j >> 4) > (i >> 4);
+    const float t0v = upper ? 0.f : Tm[i * kLdF + j];
+    const float t1v = upper ? 0.f : Tm[i * kLdF + j + 1];
+    const float b0v = t0v * be[j], b1v = t1v * be[j + 1];
+    *reinterpret_cast<uint32_t*>(Tb + i * kLdC + j) = pack_bf16(b0v, b1v);
+    *reinterpret_cast<uint32_t*>(Tw + i * kLdC + j) = pack_bf16(b0v * eg[j], b1v * eg[j + 1]);
   }
   __syncthreads();
   // ---- W = Tw K (stored negated), U = Tb V for this warp's 16 token rows
@@ -1322,6 +1372,9 @@ extern "C" int va_gdn_prefill(const VaGdnPrefill* a, va_stream_t stream) {
     // two passes: the state-independent half of every chunk in parallel, then the states in order
     if (a->num_tokens <= 0 || a->scratch_bytes < va_gdn_prefill_scratch_bytes(a->num_tokens, a->num_v_heads) ||
         (reinterpret_cast<uintptr_t>(a->scratch) & 15))
+      return VA_ERR_BAD_ARG;
+    // the rows of q / k / v are fetched as 16-byte pieces
+    if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v)) & 15)
       return VA_ERR_BAD_ARG;
     const int64_t hn = static_cast<int64_t>(a->num_v_heads) * a->num_tokens;
     __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a->scratch);

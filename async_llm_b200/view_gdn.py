@@ -605,7 +605,8 @@ class SharedCacheGDN:
               final_state=None, engine="scan", buffers=None):
         if not q.is_cuda:
             raise RuntimeError("the GDN scan kernel needs CUDA tensors: there is no CPU fallback")
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        # dense rows, fetched by the chunk engines as 16-byte pieces
+        q, k, v = (t if t.data_ptr() % 16 == 0 else t.clone() for t in (q.contiguous(), k.contiguous(), v.contiguous()))
         g32, b32 = g.float().contiguous(), beta.float().contiguous()
         N = q.shape[0]
         out = torch.empty(N, self.num_heads, self.head_v_dim, dtype=v.dtype, device=v.device)

@@ -896,6 +896,9 @@ def main() -> None:
     n_kern = 200
     kern_avg_ms = phase_ms(2 | 4, n_kern)                 # streaming pass only
     dense_ms = phase_ms(1 | 2, n_kern) if plan.groups is not None else None   # shared-block tiles only
+    # where the rest of the step goes: the same call with passes left out (no store kernel in these)
+    phases = {"stream": kern_avg_ms, "dense_tiles": dense_ms, "stream_and_merge": phase_ms(4, n_kern),
+              "stream_tiles_merge": phase_ms(0, n_kern)}
     # bytes the streaming kernel itself must read: the (row, kv head) key ranges in its items
     stream_keys = int(plan.host["items"][:, 2].sum()) if plan.num_items else 0
     algo_bytes = stream_keys * 2 * case.head_dim * 2
@@ -1020,7 +1023,7 @@ def main() -> None:
                          "kernel": f"view_decode_stream_kernel<{args.head_dim}>", "kernel_ms": kern_avg_ms,
                          "algorithmic_bytes": algo_bytes,
                          "stream_sms": plan.struct.num_lanes // (4 if args.head_dim == 256 else 6),
-                         "dense_tiles_ms": dense_ms,
+                         "dense_tiles_ms": dense_ms, "phases_ms": phases,
                          "dense_tiles_traffic": NCU_STEP_TRAFFIC["view_dense_tc_kernel"] if default_workload else None,
                          "step_compulsory_bytes": step_bytes,
                          "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm"]},

@@ -277,7 +277,7 @@ int va_gdn_compose(const int64_t* chain_a, const int64_t* chain_b, float* state,
  * chunk_gated_delta_rule + capture (models/qwen3_5_delta.py:41-121, :349-441) and the joint
  * pass of GDNPrefillBuffers.core_and_capture shared_cache/gdn_prefill.py:63-85. */
 typedef struct VaGdnPrefill {
-  const void* q;            /* bf16 [N, num_k_heads, 128]                          */
+  const void* q;            /* bf16 [N, num_k_heads, 128]; q, k, v 16-byte aligned for the CHUNK engines */
   const void* k;
   const void* v;            /* bf16 [N, num_v_heads, 128]                          */
   const float* g;           /* fp32 [N, num_v_heads]                               */
