@@ -627,7 +627,7 @@ __device__ __forceinline__ void frag_b_kn(uint32_t (&b)[4], uint32_t base, int l
 // stays in the accumulator registers of its sixteen warps for the whole block (a 16 x 64 tile each)
 // and is rounded to bf16 into shared memory once per chunk as the B operand of W X and Q X.
 struct PreSmem {
-  // 72.75 KB, so that three CTAs (12 warps) share an SM.  Regions are reused as the phases go:
+  // 72.5 KB, so that three CTAs (12 warps) share an SM.  Regions are reused as the phases go:
   //   Q tile  -> L (fp32)          once Q K^T has been taken (a CTA-wide barrier in between)
   //   L + scratch of the inverse -> T diag(beta) and T diag(beta e^gc) (bf16) once T is complete
   static constexpr int kKs = 0;
@@ -639,7 +639,7 @@ struct PreSmem {
   static constexpr int kTb = kQs;
   static constexpr int kTw = kTb + kC * kLdC * 2;
   static constexpr int kVec = kScr + 4 * 16 * 17 * 4;
-  static constexpr int kTotal = kVec + 5 * kC * 4;
+  static constexpr int kTotal = kVec + 4 * kC * 4;
   static_assert(kC * kLdF * 4 <= kC * kLdD * 2, "L fits in the Q tile");
   static_assert(kTw + kC * kLdC * 2 <= kVec, "T diag(beta) tiles fit in L + scratch");
 };
@@ -657,8 +657,7 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
   float* Lm = reinterpret_cast<float*>(csm + Sm::kL);
   float* Tm = reinterpret_cast<float*>(csm + Sm::kT);
   float* be = reinterpret_cast<float*>(csm + Sm::kVec);
-  float* gg = be + kC;
-  float* gc = gg + kC;
+  float* gc = be + kC;
   float* eg = gc + kC;
   float* ed = eg + kC;
   const int h = blockIdx.y;
@@ -698,10 +697,39 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
       cp_async16(dst, src + ch * 8, live ? 16 : 0);
     }
     cp_async_commit();
-    if (tid < kC) {
-      const int64_t tok = static_cast<int64_t>(t0) + tid;
-      be[tid] = tok < t_end ? p.beta[tok * p.num_v_heads + h] : 0.f;
-      gg[tid] = tok < t_end ? p.g[tok * p.num_v_heads + h] : 0.f;
+    if (warp == 0) {
+      // while the rows are in flight: inclusive scan of g over the 64 tokens, two per lane
+      const int64_t tok = static_cast<int64_t>(t0) + 2 * lane;
+      const float a = tok < t_end ? p.g[tok * p.num_v_heads + h] : 0.f;
+      const float b = tok + 1 < t_end ? p.g[(tok + 1) * p.num_v_heads + h] : 0.f;
+      float s = a + b;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float o = __shfl_up_sync(0xffffffffu, s, off);
+        if (lane >= off) s += o;
+      }
+      const float hi = s, lo = s - b;
+      const float tail = __shfl_sync(0xffffffffu, s, 31);
+      const float e_lo = __expf(lo), e_hi = __expf(hi);
+      const float d_lo = __expf(tail - lo), d_hi = __expf(tail - hi);
+      gc[2 * lane] = lo;
+      gc[2 * lane + 1] = hi;
+      eg[2 * lane] = e_lo;
+      eg[2 * lane + 1] = e_hi;
+      ed[2 * lane] = d_lo;
+      ed[2 * lane + 1] = d_hi;
+      if (tok < t_end) {
+        p.s_eg[hN + tok] = e_lo;
+        p.s_ed[hN + tok] = d_lo;
+      }
+      if (tok + 1 < t_end) {
+        p.s_eg[hN + tok + 1] = e_hi;
+        p.s_ed[hN + tok + 1] = d_hi;
+      }
+    } else if (warp <= 2) {
+      const int i = tid - 32;
+      const int64_t tok = static_cast<int64_t>(t0) + i;
+      be[i] = tok < t_end ? p.beta[tok * p.num_v_heads + h] : 0.f;
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -766,32 +794,6 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
     }
   }
   __syncthreads();
-  if (warp == 0) {   // inclusive scan of g over the 64 tokens, two per lane
-    const float a = gg[2 * lane], b = gg[2 * lane + 1];
-    float s = a + b;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const float o = __shfl_up_sync(0xffffffffu, s, off);
-      if (lane >= off) s += o;
-    }
-    const float hi = s, lo = s - b;
-    const float tail = __shfl_sync(0xffffffffu, s, 31);
-    gc[2 * lane] = lo;
-    gc[2 * lane + 1] = hi;
-    eg[2 * lane] = __expf(lo);
-    eg[2 * lane + 1] = __expf(hi);
-    ed[2 * lane] = __expf(tail - lo);
-    ed[2 * lane + 1] = __expf(tail - hi);
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int64_t tok = static_cast<int64_t>(t0) + 2 * lane + u;
-      if (tok < t_end) {
-        p.s_eg[hN + tok] = u == 0 ? __expf(lo) : __expf(hi);
-        p.s_ed[hN + tok] = u == 0 ? __expf(tail - lo) : __expf(tail - hi);
-      }
-    }
-  }
-  __syncthreads();
 
   // ---- K K^T and Q K^T for this warp's 16 rows; L (fp32) and the causal score tile P (bf16, out)
   {
@@ -808,6 +810,7 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
       frag_a(aq, sb + Sm::kQs, kLdD, 16 * warp, 16 * ks, lane);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
+        if (np > warp) continue;   // columns past this warp's rows are masked out (j > i): left at zero
         uint32_t b[4];
         frag_b_nk(b, sb + Sm::kKs, kLdD, 16 * np, 16 * ks, lane);
         const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
@@ -821,13 +824,15 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
     const int i0 = 16 * warp + g;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
+      if (nt < 2 * (warp + 1)) {   // blocks of L above the diagonal are never read; P is zero there
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = i0 + (e >> 1) * 8;
-        const int j = 8 * nt + 2 * t + (e & 1);
-        const float dec = j <= i ? __expf(gc[i] - gc[j]) : 0.f;
-        Lm[i * kLdF + j] = j < i ? -be[i] * kk[nt][e] * dec : 0.f;
-        qk[nt][e] *= dec;
+        for (int e = 0; e < 4; ++e) {
+          const int i = i0 + (e >> 1) * 8;
+          const int j = 8 * nt + 2 * t + (e & 1);
+          const float dec = j <= i ? __expf(gc[i] - gc[j]) : 0.f;
+          Lm[i * kLdF + j] = j < i ? -be[i] * kk[nt][e] * dec : 0.f;
+          qk[nt][e] *= dec;
+        }
       }
       if (t0 + i0 < t_end)
         *reinterpret_cast<uint32_t*>(p.s_p + (hN + t0 + i0) * kC + 8 * nt + 2 * t) = pack_bf16(qk[nt][0], qk[nt][1]);
@@ -902,9 +907,9 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
 #pragma unroll 4
   for (int idx = tid; idx < kC * kC / 2; idx += 128) {
     const int i = idx / (kC / 2), j = 2 * (idx - i * (kC / 2));
-    const bool upper = (j >> 4) > (i >> 4);
-    const float t0v = upper ? 0.f : Tm[i * kLdF + j];
-    const float t1v = upper ? 0.f : Tm[i * kLdF + j + 1];
+    if ((j >> 4) > (i >> 4)) continue;   // blocks above the diagonal are zero and never multiplied
+    const float t0v = Tm[i * kLdF + j];
+    const float t1v = Tm[i * kLdF + j + 1];
     const float b0v = t0v * be[j], b1v = t1v * be[j + 1];
     *reinterpret_cast<uint32_t*>(Tb + i * kLdC + j) = pack_bf16(b0v, b1v);
     *reinterpret_cast<uint32_t*>(Tw + i * kLdC + j) = pack_bf16(b0v * eg[j], b1v * eg[j + 1]);
@@ -920,6 +925,7 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
     }
 #pragma unroll
     for (int ks = 0; ks < kC / 16; ++ks) {
+      if (ks > warp) continue;   // T is lower triangular: no contribution from later tokens
       uint32_t aw[4], au[4];
       frag_a(aw, sb + Sm::kTw, kLdC, 16 * warp, 16 * ks, lane);
       frag_a(au, sb + Sm::kTb, kLdC, 16 * warp, 16 * ks, lane);
