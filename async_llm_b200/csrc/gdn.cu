@@ -327,12 +327,14 @@ struct ComposeParams {
   int32_t num_heads;
 };
 
-// grid (H, W), 256 threads; X (dv x dk) and its successor in shared memory (2 x 64 KB).
-// Thread (ty, tx) owns the 8x8 block rows 8ty.., cols 8tx.. of X A_j + B_j.
+// grid (H, W), 256 threads; X (dv x dk), its successor and the level's A_j in shared memory
+// (3 x 64 KB).  Thread (ty, tx) owns the 8x8 block rows 8ty.., cols 8tx.. of X A_j + B_j and sums
+// over i in ascending order.  (With A_j's rows read from global memory inside the loop a level took
+// 146 us for 256 (worker, head) pairs, a tenth of the fp32 rate: every step waited for its row.)
 template <bool kBf16>
 __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant__ ComposeParams p) {
   using IO = SumIO<kBf16>;
-  extern __shared__ __align__(16) float xs[];  // 2 * 128 * 128
+  extern __shared__ __align__(16) float xs[];  // 3 * 128 * 128
   const int h = blockIdx.x;
   const int w = blockIdx.y;
   const int tid = threadIdx.x;
@@ -341,6 +343,7 @@ __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant_
   const int64_t head_off = static_cast<int64_t>(h) * kD * kD;
   float* cur = xs;
   float* nxt = xs + kD * kD;
+  float* as = xs + 2 * kD * kD;
   bool have = false;
   for (int j = 0; j < p.depth; ++j) {
     const void* aj = reinterpret_cast<const void*>(p.chain_a[static_cast<int64_t>(w) * p.depth + j]);
@@ -354,20 +357,32 @@ __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant_
       __syncthreads();
       continue;
     }
+    // A_j (widened) to shared memory, 16 pieces of four values per thread in flight
+#pragma unroll 4
+    for (int i = tid * 4; i < kD * kD; i += 256 * 4)
+      *reinterpret_cast<float4*>(as + i) = IO::widen(IO::ld(aj, head_off + i));
+    __syncthreads();
     float acc[8][8];
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
       for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
-    for (int i = 0; i < kD; ++i) {
-      const float4 a0 = IO::widen(IO::ld(aj, head_off + static_cast<int64_t>(i) * kD + tx * 8));
-      const float4 a1 = IO::widen(IO::ld(aj, head_off + static_cast<int64_t>(i) * kD + tx * 8 + 4));
-      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll 1
+    for (int i0 = 0; i0 < kD; i0 += 4) {
+      float4 xv[8];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float x = cur[(ty * 8 + r) * kD + i];
+      for (int r = 0; r < 8; ++r) xv[r] = *reinterpret_cast<const float4*>(cur + (ty * 8 + r) * kD + i0);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(x, av[c], acc[r][c]);
+      for (int ii = 0; ii < 4; ++ii) {
+        const float4 a0 = *reinterpret_cast<const float4*>(as + (i0 + ii) * kD + tx * 8);
+        const float4 a1 = *reinterpret_cast<const float4*>(as + (i0 + ii) * kD + tx * 8 + 4);
+        const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const float x = ii == 0 ? xv[r].x : ii == 1 ? xv[r].y : ii == 2 ? xv[r].z : xv[r].w;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(x, av[c], acc[r][c]);
+        }
       }
     }
 #pragma unroll
@@ -627,31 +642,33 @@ __device__ __forceinline__ void frag_b_kn(uint32_t (&b)[4], uint32_t base, int l
 // stays in the accumulator registers of its sixteen warps for the whole block (a 16 x 64 tile each)
 // and is rounded to bf16 into shared memory once per chunk as the B operand of W X and Q X.
 struct PreSmem {
-  // 72.5 KB, so that three CTAs (12 warps) share an SM.  Regions are reused as the phases go:
+  // 56 KB, so that four CTAs (16 warps) share an SM.  Regions are reused as the phases go:
   //   Q tile  -> L (fp32)          once Q K^T has been taken (a CTA-wide barrier in between)
   //   L + scratch of the inverse -> T diag(beta) and T diag(beta e^gc) (bf16) once T is complete
+  //   T (fp32) -> the V tile, fetched once T has been converted (V is only needed for U, at the end)
+  static constexpr int kTile = kC * kLdD * 2;                  // one [C][128] bf16 tile
   static constexpr int kKs = 0;
-  static constexpr int kVs = kKs + kC * kLdD * 2;
-  static constexpr int kT = kVs + kC * kLdD * 2;
-  static constexpr int kQs = kT + kC * kLdF * 4;
+  static constexpr int kT = kKs + kTile;
+  static constexpr int kVs = kT;
+  static constexpr int kQs = kT + kTile;
   static constexpr int kL = kQs;
-  static constexpr int kScr = kQs + kC * kLdD * 2;          // 4 x 16 x 17 fp32 of the block inverse
+  static constexpr int kScr = kQs + kTile;                     // 4 x 16 x 16 fp32 of the block inverse
   static constexpr int kTb = kQs;
   static constexpr int kTw = kTb + kC * kLdC * 2;
-  static constexpr int kVec = kScr + 4 * 16 * 17 * 4;
+  static constexpr int kVec = kScr + 4 * 16 * 16 * 4;
   static constexpr int kTotal = kVec + 4 * kC * 4;
-  static_assert(kC * kLdF * 4 <= kC * kLdD * 2, "L fits in the Q tile");
+  static_assert(kC * kLdF * 4 <= kTile, "L fits in the Q tile, T in the V tile");
   static_assert(kTw + kC * kLdC * 2 <= kVec, "T diag(beta) tiles fit in L + scratch");
+  static_assert(4 * (kTotal + 1024) <= 228 * 1024, "four CTAs per SM");
 };
 
 // grid (chunk, Hv, R), 128 threads
-__global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_constant__ ScanParams p) {
+__global__ void __launch_bounds__(128, 4) gdn_chunk_pre_kernel(const __grid_constant__ ScanParams p) {
   extern __shared__ __align__(128) unsigned char csm[];
   using Sm = PreSmem;
   const uint32_t sb = smem_u32(csm);
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kKs);
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kQs);
-  __nv_bfloat16* Vs = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kVs);
   __nv_bfloat16* Tb = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kTb);
   __nv_bfloat16* Tw = reinterpret_cast<__nv_bfloat16*>(csm + Sm::kTw);
   float* Lm = reinterpret_cast<float*>(csm + Sm::kL);
@@ -673,28 +690,26 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
   if (t0 >= t_end) return;
   const int64_t hN = static_cast<int64_t>(h) * p.num_tokens;
 
-  // ---- stage: the raw K, Q and V rows of the chunk go straight to their shared-memory tiles as
-  //      16-byte asynchronous copies (3072 of them, 24 per thread, all in flight at once); rows past
-  //      the end are zero-filled.  (Register loads did not do: with 218 KB of the SM's 256 KB taken
-  //      as shared memory by the three resident CTAs the L1 keeps few lines for misses in flight,
+  // ---- stage: the raw K and Q rows of the chunk go straight to their shared-memory tiles as
+  //      16-byte asynchronous copies (2048 of them, 16 per thread, all in flight at once); rows past
+  //      the end are zero-filled.  (Register loads did not do: with most of the SM's 256 KB taken
+  //      as shared memory by the resident CTAs the L1 keeps few lines for misses in flight,
   //      and a warp's 48 row loads took 10 us.)  The rows are then normalised in place.
   {
     constexpr int kRowChunks = kD / 8;              // 16-byte chunks of a row
     constexpr int kTileChunks = kC * kRowChunks;
 #pragma unroll
-    for (int j = 0; j < 3 * kTileChunks / 128; ++j) {
+    for (int j = 0; j < 2 * kTileChunks / 128; ++j) {
       const int idx = tid + 128 * j;
-      const int which = idx / kTileChunks;          // 0 = K, 1 = Q, 2 = V (uniform per j)
+      const int which = idx / kTileChunks;          // 0 = K, 1 = Q (uniform per j)
       const int rem = idx - which * kTileChunks;
       const int i = rem / kRowChunks;
       const int ch = rem - i * kRowChunks;
       const int64_t tok = static_cast<int64_t>(t0) + i;
       const bool live = tok < t_end;
       const int64_t row = live ? tok : static_cast<int64_t>(t0);
-      const __nv_bfloat16* src = which == 2 ? p.v + (row * p.num_v_heads + h) * kD
-                                            : (which == 0 ? p.k : p.q) + (row * p.num_k_heads + hk) * kD;
-      const uint32_t dst = sb + (which == 0 ? Sm::kKs : which == 1 ? Sm::kQs : Sm::kVs) + (i * kLdD + ch * 8) * 2;
-      cp_async16(dst, src + ch * 8, live ? 16 : 0);
+      const __nv_bfloat16* src = (which == 0 ? p.k : p.q) + (row * p.num_k_heads + hk) * kD;
+      cp_async16(sb + (which == 0 ? Sm::kKs : Sm::kQs) + (i * kLdD + ch * 8) * 2, src + ch * 8, live ? 16 : 0);
     }
     cp_async_commit();
     if (warp == 0) {
@@ -869,7 +884,8 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
   }
   __syncthreads();
   {
-    float* scratch = reinterpret_cast<float*>(csm + Sm::kScr) + warp * 16 * 17;
+    // per-warp 16 x 16 staging tile; row r keeps its columns rotated by r (conflict-light stores)
+    float* scratch = reinterpret_cast<float*>(csm + Sm::kScr) + warp * 16 * 16;
     const int rr = lane >> 1, c0 = (lane & 1) * 8;
     for (int d = 1; d < 4; ++d) {
       if (warp < 4 - d) {
@@ -886,7 +902,7 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
           }
         }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) scratch[rr * 17 + c0 + e] = s[e];
+        for (int e = 0; e < 8; ++e) scratch[rr * 16 + ((c0 + e + rr) & 15)] = s[e];
         __syncwarp();
         float o[8];
 #pragma unroll
@@ -895,7 +911,7 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
         for (int k = 0; k < 16; ++k) {
           const float a = Tm[(16 * I + rr) * kLdF + 16 * I + k];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] = fmaf(a, scratch[k * 17 + c0 + e], o[e]);
+          for (int e = 0; e < 8; ++e) o[e] = fmaf(a, scratch[k * 16 + ((c0 + e + k) & 15)], o[e]);
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) Tm[(16 * I + rr) * kLdF + 16 * J + c0 + e] = o[e];
@@ -915,44 +931,59 @@ __global__ void __launch_bounds__(128, 3) gdn_chunk_pre_kernel(const __grid_cons
     *reinterpret_cast<uint32_t*>(Tw + i * kLdC + j) = pack_bf16(b0v * eg[j], b1v * eg[j + 1]);
   }
   __syncthreads();
-  // ---- W = Tw K (stored negated), U = Tb V for this warp's 16 token rows
+  // ---- T (fp32) is dead: the V rows go to its place while W is formed
   {
-    float w[16][4], u[16][4];
+    constexpr int kRowChunks = kD / 8;
+#pragma unroll
+    for (int j = 0; j < kC * kRowChunks / 128; ++j) {
+      const int idx = tid + 128 * j;
+      const int i = idx / kRowChunks;
+      const int ch = idx - i * kRowChunks;
+      const int64_t tok = static_cast<int64_t>(t0) + i;
+      const bool live = tok < t_end;
+      const int64_t row = live ? tok : static_cast<int64_t>(t0);
+      cp_async16(sb + Sm::kVs + (i * kLdD + ch * 8) * 2, p.v + (row * p.num_v_heads + h) * kD + ch * 8, live ? 16 : 0);
+    }
+    cp_async_commit();
+  }
+  // ---- W = Tw K (stored negated), then U = Tb V, for this warp's 16 token rows
+  const int64_t tok0 = static_cast<int64_t>(t0) + 16 * warp + g;
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    if (pass == 1) {
+      cp_async_wait<0>();
+      __syncthreads();
+    }
+    const uint32_t a_tile = sb + (pass == 0 ? Sm::kTw : Sm::kTb);
+    const uint32_t b_tile = sb + (pass == 0 ? Sm::kKs : Sm::kVs);
+    float acc[16][4];
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) w[nt][e] = u[nt][e] = 0.f;
+      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
     }
 #pragma unroll
     for (int ks = 0; ks < kC / 16; ++ks) {
       if (ks > warp) continue;   // T is lower triangular: no contribution from later tokens
-      uint32_t aw[4], au[4];
-      frag_a(aw, sb + Sm::kTw, kLdC, 16 * warp, 16 * ks, lane);
-      frag_a(au, sb + Sm::kTb, kLdC, 16 * warp, 16 * ks, lane);
+      uint32_t a[4];
+      frag_a(a, a_tile, kLdC, 16 * warp, 16 * ks, lane);
 #pragma unroll
       for (int np = 0; np < 8; ++np) {
-        uint32_t b[4], c[4];
-        frag_b_kn(b, sb + Sm::kKs, kLdD, 16 * ks, 16 * np, lane);
-        frag_b_kn(c, sb + Sm::kVs, kLdD, 16 * ks, 16 * np, lane);
+        uint32_t b[4];
+        frag_b_kn(b, b_tile, kLdD, 16 * ks, 16 * np, lane);
         const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
-        const uint32_t c0[2] = {c[0], c[1]}, c1[2] = {c[2], c[3]};
-        mma_bf16_16816(w[2 * np], aw, b0);
-        mma_bf16_16816(w[2 * np + 1], aw, b1);
-        mma_bf16_16816(u[2 * np], au, c0);
-        mma_bf16_16816(u[2 * np + 1], au, c1);
+        mma_bf16_16816(acc[2 * np], a, b0);
+        mma_bf16_16816(acc[2 * np + 1], a, b1);
       }
     }
-    const int64_t tok0 = static_cast<int64_t>(t0) + 16 * warp + g;
+    __nv_bfloat16* dst = pass == 0 ? p.s_w : p.s_u;
+    const float sign = pass == 0 ? -1.f : 1.f;
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt) {
-      if (tok0 < t_end) {
-        *reinterpret_cast<uint32_t*>(p.s_w + (hN + tok0) * kD + 8 * nt + 2 * t) = pack_bf16(-w[nt][0], -w[nt][1]);
-        *reinterpret_cast<uint32_t*>(p.s_u + (hN + tok0) * kD + 8 * nt + 2 * t) = pack_bf16(u[nt][0], u[nt][1]);
-      }
-      if (tok0 + 8 < t_end) {
-        *reinterpret_cast<uint32_t*>(p.s_w + (hN + tok0 + 8) * kD + 8 * nt + 2 * t) = pack_bf16(-w[nt][2], -w[nt][3]);
-        *reinterpret_cast<uint32_t*>(p.s_u + (hN + tok0 + 8) * kD + 8 * nt + 2 * t) = pack_bf16(u[nt][2], u[nt][3]);
-      }
+      if (tok0 < t_end)
+        *reinterpret_cast<uint32_t*>(dst + (hN + tok0) * kD + 8 * nt + 2 * t) = pack_bf16(sign * acc[nt][0], sign * acc[nt][1]);
+      if (tok0 + 8 < t_end)
+        *reinterpret_cast<uint32_t*>(dst + (hN + tok0 + 8) * kD + 8 * nt + 2 * t) = pack_bf16(sign * acc[nt][2], sign * acc[nt][3]);
     }
   }
 }
@@ -1316,7 +1347,7 @@ extern "C" int va_gdn_compose(const int64_t* chain_a, const int64_t* chain_b, fl
   p.num_workers = num_workers;
   p.depth = depth;
   p.num_heads = num_heads;
-  const int smem = 2 * kD * kD * static_cast<int>(sizeof(float));
+  const int smem = 3 * kD * kD * static_cast<int>(sizeof(float));
   auto kernel = summary_dtype == VA_SUMMARY_BF16 ? gdn_compose_kernel<true> : gdn_compose_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return va_host::note_cuda_error(e);

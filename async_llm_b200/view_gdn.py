@@ -586,6 +586,10 @@ class SharedCacheGDN:
         self._step["segments"] = segments
         if buffers is not None:
             buffers.load_segments(segments)
+        else:
+            # once per forward, from pinned memory: a copy from pageable memory would wait for the
+            # stream's earlier kernels and serialise the host behind the GPU
+            self._step["seg_d"] = self._upload_i32(np.concatenate(([0], np.cumsum(segments))))
         self.prefill_buffers = buffers
         self._prepared_prefill = True
         self.prepare_count += 1
@@ -594,6 +598,13 @@ class SharedCacheGDN:
         if self._prepared_prefill:
             self._publish(success)
             self._prepared_prefill = False
+
+    def _upload_i32(self, values) -> torch.Tensor:
+        """A small host array as an int32 device tensor, staged through pinned memory."""
+        host = torch.from_numpy(np.ascontiguousarray(values, dtype=np.int32))
+        if self.device.type != "cuda":
+            return host
+        return host.pin_memory().to(self.device, non_blocking=True)
 
     def _init_rows(self) -> torch.Tensor:
         """Rows (read a, read b, write a, write b) of a layer's ``[6, W]`` address list."""
@@ -617,9 +628,17 @@ class SharedCacheGDN:
                 raise ValueError(f"{N} token rows exceed the prepared capacity {buffers.rows}")
             seg_d = buffers.seg
         else:
-            seg = torch.tensor(np.concatenate(([0], np.cumsum(segments))), dtype=torch.int32)
-            seg_d = seg.to(self.device, non_blocking=True)
-        init_t = init if isinstance(init, torch.Tensor) else torch.from_numpy(init).to(self.device)
+            st = self._step
+            if st is not None and segments is st.get("segments") and st.get("seg_d") is not None:
+                seg_d = st["seg_d"]          # the prepared forward's own offsets, uploaded once
+            else:
+                seg_d = self._upload_i32(np.concatenate(([0], np.cumsum(segments))))
+        if isinstance(init, torch.Tensor):
+            init_t = init
+        else:
+            init_t = torch.from_numpy(init)
+            if self.device.type == "cuda":
+                init_t = init_t.pin_memory().to(self.device, non_blocking=True)
         a = _lib.VaGdnPrefill()
         a.q, a.k, a.v, a.g, a.beta, a.out = (t.data_ptr() for t in (q, k, v, g32, b32, out))
         a.seg_off = seg_d.data_ptr()
@@ -672,9 +691,8 @@ class SharedCacheGDN:
         if buffers is not None:
             seg_d = buffers.seg
         else:
-            seg = torch.tensor(np.concatenate(([0], np.cumsum(st["segments"]))), dtype=torch.int32)
-            assert int(seg[-1]) == N, "prefill segments do not cover the batch"
-            seg_d = seg.to(self.device, non_blocking=True)
+            assert sum(st["segments"]) == N, "prefill segments do not cover the batch"
+            seg_d = st["seg_d"]
         qkv_out = torch.empty(N, self.conv_dim, dtype=torch.bfloat16, device=self.device)
         if buffers is not None:
             qkv_out.zero_()    # rows beyond the planned batch are not written by the kernel
