@@ -882,16 +882,21 @@ def main() -> None:
                                                dv.attn.status().data_ptr(), _lib.stream_ptr())
         plan.struct.phase_mask = 0
         _lib.check(rc, "va_view_decode")
-        for _ in range(3):
+        for _ in range(10):
             g.replay()
         torch.cuda.synchronize()
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record()
-        for _ in range(iters):
-            g.replay()
-        k1.record()
-        k1.synchronize()
-        return k0.elapsed_time(k1) / iters
+        # five rounds of back-to-back replays, each between two events; the median round
+        per_round = max(iters // 5, 1)
+        rounds_ms = []
+        for _ in range(5):
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record()
+            for _ in range(per_round):
+                g.replay()
+            k1.record()
+            k1.synchronize()
+            rounds_ms.append(k0.elapsed_time(k1) / per_round)
+        return statistics.median(rounds_ms)
 
     n_kern = 200
     kern_avg_ms = phase_ms(2 | 4, n_kern)                 # streaming pass only
