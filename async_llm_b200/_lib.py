@@ -216,6 +216,9 @@ SIGNATURES = {
     "va_plan_decode": (C.c_int, [C.POINTER(VaPlanParams), C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                  C.c_int64, C.POINTER(VaPlanLayout)]),
+    "va_gdn_plan_tables": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                     C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                     C.c_int32, C.c_int32, C.c_void_p]),
     "va_plan_prefill_tiles": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                         C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
     "va_block_copy": (C.c_int, [C.POINTER(VaPool), C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_int32,

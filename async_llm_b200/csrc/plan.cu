@@ -537,3 +537,46 @@ extern "C" int va_plan_prefill_tiles(const int32_t* segments, int32_t num_segmen
   }
   return VA_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Address tables of a GDN forward (host code, no CUDA call): see va_gdn_plan_tables in the header.
+// tab[row][layer][worker][position]; rows 2..7 use position 0 only.
+extern "C" int va_gdn_plan_tables(const int64_t* block_addr, const int64_t* block_conv, const int32_t* chain_idx,
+                                  const int32_t* target_idx, const int64_t* write_a_base, int64_t write_a_stride,
+                                  const int64_t* write_b_base, int64_t write_b_stride,
+                                  const int64_t* conv_write_base, int64_t conv_write_stride, int32_t num_blocks,
+                                  int32_t layers, int32_t workers, int32_t depth, int64_t* tab) {
+  if (num_blocks < 0 || layers <= 0 || workers < 0 || depth <= 0 || tab == nullptr) return VA_ERR_BAD_ARG;
+  if (workers > 0 && (block_addr == nullptr || chain_idx == nullptr || target_idx == nullptr)) return VA_ERR_BAD_ARG;
+  const int64_t L = layers, W = workers, Dp = depth;
+  const int64_t plane = L * W * Dp;
+  std::memset(tab, 0, sizeof(int64_t) * 8 * plane);
+  for (int64_t w = 0; w < W; ++w) {
+    const int32_t* chain = chain_idx + w * Dp;
+    for (int64_t j = 0; j < Dp; ++j)
+      if (chain[j] < 0 || chain[j] > num_blocks) return VA_ERR_BAD_ARG;
+    const int32_t target = target_idx[w];
+    if (target < 0 || target > num_blocks) return VA_ERR_BAD_ARG;
+    for (int64_t l = 0; l < L; ++l) {
+      int64_t* at = tab + (l * W + w) * Dp;   // [row 0][l][w][0]
+      int64_t conv = 0;
+      for (int64_t j = 0; j < Dp; ++j) {
+        const int64_t* pair = block_addr + (static_cast<int64_t>(chain[j]) * L + l) * 2;
+        at[j] = pair[0];
+        at[plane + j] = pair[1];
+        if (block_conv != nullptr) {
+          const int64_t c = block_conv[static_cast<int64_t>(chain[j]) * L + l];
+          if (c != 0) conv = c;   // the last block of the chain that has a window
+        }
+      }
+      const int64_t* tp = block_addr + (static_cast<int64_t>(target) * L + l) * 2;
+      at[2 * plane] = tp[0];
+      at[3 * plane] = tp[1];
+      at[4 * plane] = conv;
+      if (write_a_base != nullptr) at[5 * plane] = write_a_base[w] + l * write_a_stride;
+      if (write_b_base != nullptr) at[6 * plane] = write_b_base[w] + l * write_b_stride;
+      if (conv_write_base != nullptr) at[7 * plane] = conv_write_base[w] + l * conv_write_stride;
+    }
+  }
+  return VA_OK;
+}

@@ -291,46 +291,44 @@ class SharedCacheGDN:
             for j, block in enumerate(chain):
                 chain_idx[w, j] = number(block)
             target_idx[w] = number(targets[w])
-        addr = np.stack(rows)                                     # [blocks + 1, L, 2]
-        tab = np.zeros((8, layers, W, depth), dtype=np.int64)
-        tab[ROW_CHAIN_A] = addr[chain_idx, :, 0].transpose(2, 0, 1)
-        tab[ROW_CHAIN_B] = addr[chain_idx, :, 1].transpose(2, 0, 1)
-        tab[ROW_READ_A, :, :, 0] = addr[target_idx, :, 0].T
-        tab[ROW_READ_B, :, :, 0] = addr[target_idx, :, 1].T
+        addr = np.ascontiguousarray(np.stack(rows))               # [blocks + 1, L, 2]
+        conv_addr = np.ascontiguousarray(np.stack(conv_rows)) if with_outputs else None   # [blocks + 1, L]
+        chain32 = np.ascontiguousarray(chain_idx, dtype=np.int32)
+        target32 = np.ascontiguousarray(target_idx, dtype=np.int32)
         out_a = out_b = conv_out = None
+        bases = [None, None, None]          # per-worker addresses of layer 0: write a, write b, conv write
+        strides = [0, 0, 0]                 # bytes between a worker's layers
         if with_outputs:
             H, dk, dv = self.num_heads, self.head_k_dim, self.head_v_dim
-            # most recent conv window along each chain (minisgl/shared_cache/gdn.py:182-207): the last
-            # block of the chain that has one, per layer
-            caddr = np.stack(conv_rows)[chain_idx]                       # [W, depth, L]
-            has = caddr != 0
-            last = depth - 1 - np.argmax(has[:, ::-1, :], axis=1)        # [W, L]
-            picked = np.take_along_axis(caddr, last[:, None, :], axis=1)[:, 0, :]
-            tab[ROW_CONV_READ, :, :, 0] = np.where(has.any(axis=1), picked, 0).T
             conv_out = [torch.empty(layers, self.conv_dim, self.conv_kernel, dtype=torch.bfloat16,
                                     device=self.device) for _ in targets]
-            conv_stride = self.conv_dim * self.conv_kernel * 2
-            tab[ROW_CONV_WRITE, :, :, 0] = (np.fromiter((t.data_ptr() for t in conv_out), np.int64, W)[None, :]
-                                            + np.arange(layers, dtype=np.int64)[:, None] * conv_stride)
+            bases[2] = np.fromiter((t.data_ptr() for t in conv_out), np.int64, W)
+            strides[2] = self.conv_dim * self.conv_kernel * 2
             # one all-layer allocation per worker: a stopped worker must not pin a whole batch
-            steps = np.arange(layers, dtype=np.int64)
             if dk == dv:
                 # A_hat and B_hat of all layers of one worker in one allocation: [2 * layers, 1, H, d, d]
                 out_a = [torch.empty(2 * layers, 1, H, dk, dk, dtype=self.state_dtype, device=self.device)
                          for _ in targets]
                 out_b = None
-                base = np.fromiter((t.data_ptr() for t in out_a), np.int64, W)
                 stride = H * dk * dk * out_a[0].element_size() if W else 0
-                tab[ROW_WRITE_A, :, :, 0] = base[None, :] + steps[:, None] * stride
-                tab[ROW_WRITE_B, :, :, 0] = base[None, :] + (layers + steps[:, None]) * stride
+                bases[0] = np.fromiter((t.data_ptr() for t in out_a), np.int64, W)
+                bases[1] = bases[0] + layers * stride
+                strides[0] = strides[1] = stride
             else:
                 out_a = [torch.empty(layers, 1, H, dk, dk, dtype=self.state_dtype, device=self.device) for _ in targets]
                 out_b = [torch.empty(layers, 1, H, dv, dk, dtype=self.state_dtype, device=self.device) for _ in targets]
                 esz = out_a[0].element_size() if W else 0
-                tab[ROW_WRITE_A, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_a), np.int64, W)[None, :]
-                                             + steps[:, None] * (H * dk * dk * esz))
-                tab[ROW_WRITE_B, :, :, 0] = (np.fromiter((t.data_ptr() for t in out_b), np.int64, W)[None, :]
-                                             + steps[:, None] * (H * dv * dk * esz))
+                bases[0] = np.fromiter((t.data_ptr() for t in out_a), np.int64, W)
+                bases[1] = np.fromiter((t.data_ptr() for t in out_b), np.int64, W)
+                strides[0], strides[1] = H * dk * dk * esz, H * dv * dk * esz
+        # the tables themselves (chain rows, read / write rows, most recent conv window along each
+        # chain -- minisgl/shared_cache/gdn.py:182-207) are laid out by the native planner
+        tab = np.zeros((8, layers, W, depth), dtype=np.int64)
+        ptr = lambda a: a.ctypes.data if a is not None else None
+        rc = _lib.VA_OK if W == 0 else _lib.lib().va_gdn_plan_tables(
+            ptr(addr), ptr(conv_addr), ptr(chain32), ptr(target32), ptr(bases[0]), strides[0], ptr(bases[1]),
+            strides[1], ptr(bases[2]), strides[2], len(rows) - 1, layers, W, depth, ptr(tab))
+        _lib.check(rc, "va_gdn_plan_tables")
         if buffers is not None:
             buffers.load(tab)
             dev, rw, run_W, run_depth = buffers.tab, buffers.rw, buffers.workers, buffers.depth

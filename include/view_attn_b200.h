@@ -450,6 +450,26 @@ int va_plan_prefill_tiles(const int32_t* segments, int32_t num_segments, const i
                           int32_t* entries, int32_t num_rows, int32_t* tiles, int32_t tile_capacity,
                           int32_t* num_tiles_out);
 
+/* Address tables of a GDN forward over the views (host code, no CUDA call).  Replaces the pointer
+ * tables GDNDecodeBuffers.prepare assembles per chain level (shared_cache/gdn_decode.py:62-167:
+ * prefix_links / terminal_sinks over the chains, then per-layer pointer lists) and the
+ * "most recent conv window along the reversed chain" rule of SharedCacheGDN.prior_conv_states
+ * (shared_cache/gdn.py:182-207).  The caller numbers the distinct blocks of the step (row 0 = no
+ * block) and hands over their per-layer addresses:
+ *   block_addr [num_blocks + 1, layers, 2]  (A_hat, B_hat) of a block's summary, 0 = none
+ *   block_conv [num_blocks + 1, layers]     conv window, 0 = none; NULL = no conv / write rows
+ *   chain_idx  [workers, depth]             rows of block_addr in view order, 0 past the chain's end
+ *   target_idx [workers]                    row of each worker's write block
+ *   write_*_base [workers] + layer * write_*_stride (bytes): the fresh slabs of a worker's layers
+ * and gets `tab` [8, layers, workers, depth] int64, zero-filled and then: row 0 / 1 = chain A_hat /
+ * B_hat per view position; rows 2..7 (read a, read b, conv read, write a, write b, conv write) in
+ * [..., 0].  Conv read = the window of the LAST block of the chain that has one, per layer. */
+int va_gdn_plan_tables(const int64_t* block_addr, const int64_t* block_conv, const int32_t* chain_idx,
+                       const int32_t* target_idx, const int64_t* write_a_base, int64_t write_a_stride,
+                       const int64_t* write_b_base, int64_t write_b_stride, const int64_t* conv_write_base,
+                       int64_t conv_write_stride, int32_t num_blocks, int32_t layers, int32_t workers,
+                       int32_t depth, int64_t* tab);
+
 /* 8. Block merge / append ------------------------------------------------------------------------
  * Replaces: SharedCacheSession._copy_slots + _shift_keys_ (shared_cache/session.py:489-528), which
  * loop over the layers in Python (index_select / index_copy_ per layer for K and V, then

@@ -248,3 +248,29 @@ def prefill_tiles(seg_arr, req_segments, per_tile, H, n_ctas_cap):
     tiles[:, 0:4] = per_head[order, 1:5]
     tiles[:, 4] = heads[order]
     return entries, tiles
+
+
+def gdn_tables(block_addr, block_conv, chain_idx, target_idx, write_a, write_b, conv_write, layers):
+    """Address tables of a GDN forward by array indexing: ``[8, L, W, depth]`` int64 (rows: chain
+    A_hat, chain B_hat, read a, read b, conv read, write a, write b, conv write; rows 2..7 in
+    ``[..., 0]``).  ``write_*`` are ``(base [W], stride)`` pairs or None.  The conv window read by a
+    worker is the one of the last block of its chain that has one
+    (minisgl/shared_cache/gdn.py:182-207)."""
+    W, depth = chain_idx.shape
+    tab = np.zeros((8, layers, W, depth), np.int64)
+    tab[0] = block_addr[chain_idx, :, 0].transpose(2, 0, 1)
+    tab[1] = block_addr[chain_idx, :, 1].transpose(2, 0, 1)
+    tab[2, :, :, 0] = block_addr[target_idx, :, 0].T
+    tab[3, :, :, 0] = block_addr[target_idx, :, 1].T
+    if block_conv is not None:
+        caddr = block_conv[chain_idx]                                    # [W, depth, L]
+        has = caddr != 0
+        last = depth - 1 - np.argmax(has[:, ::-1, :], axis=1)            # [W, L]
+        picked = np.take_along_axis(caddr, last[:, None, :], axis=1)[:, 0, :]
+        tab[4, :, :, 0] = np.where(has.any(axis=1), picked, 0).T
+    steps = np.arange(layers, dtype=np.int64)
+    for row, out in ((5, write_a), (6, write_b), (7, conv_write)):
+        if out is not None:
+            base, stride = out
+            tab[row, :, :, 0] = base[None, :] + steps[:, None] * stride
+    return tab

@@ -205,3 +205,45 @@ def test_native_prefill_tile_planner_matches_the_numpy_restatement():
             rc = lib.va_plan_prefill_tiles(seg_arr.ctypes.data, seg_arr.shape[0], req_arr.ctypes.data, R, per_tile, H,
                                            n_ctas_cap, entries.ctypes.data, off, tiles.ctypes.data, cap - 1, C.byref(n))
             assert rc == _lib.VA_ERR_CAPACITY and n.value == cap
+
+
+def test_native_gdn_tables_match_the_numpy_restatement():
+    rng = np.random.default_rng(23)
+    lib = _lib.lib()
+    for case in range(60):
+        B = int(rng.integers(1, 12))
+        L = int(rng.integers(1, 5))
+        W = int(rng.integers(1, 9))
+        depth = int(rng.integers(1, 5))
+        block_addr = rng.integers(1, 1 << 40, size=(B + 1, L, 2)).astype(np.int64)
+        block_addr[rng.random((B + 1, L)) < 0.3] = 0          # blocks without a summary in a layer
+        block_addr[0] = 0
+        block_conv = rng.integers(1, 1 << 40, size=(B + 1, L)).astype(np.int64)
+        block_conv[rng.random((B + 1, L)) < 0.5] = 0
+        block_conv[0] = 0
+        chain_idx = np.zeros((W, depth), np.int32)
+        for w in range(W):
+            n = int(rng.integers(0, depth + 1))
+            chain_idx[w, :n] = rng.integers(1, B + 1, size=n)
+        target_idx = rng.integers(1, B + 1, size=W).astype(np.int32)
+        with_outputs = case % 3 != 0
+        outs = [None, None, None]
+        if with_outputs:
+            outs = [(rng.integers(1, 1 << 40, size=W).astype(np.int64), int(rng.integers(1, 1 << 20))) for _ in range(3)]
+        want = plan_numpy.gdn_tables(block_addr, block_conv if with_outputs else None, chain_idx.astype(np.int64),
+                                     target_idx.astype(np.int64), *outs, L)
+        tab = np.full((8, L, W, depth), -5, np.int64)
+        ptr = lambda a: a.ctypes.data if a is not None else None
+        base = [o[0] if o is not None else None for o in outs]
+        stride = [o[1] if o is not None else 0 for o in outs]
+        rc = lib.va_gdn_plan_tables(ptr(block_addr), ptr(block_conv) if with_outputs else None, ptr(chain_idx),
+                                    ptr(target_idx), ptr(base[0]), stride[0], ptr(base[1]), stride[1], ptr(base[2]),
+                                    stride[2], B, L, W, depth, ptr(tab))
+        assert rc == 0, case
+        assert np.array_equal(tab, want), case
+    # a block number outside the table is refused
+    bad = chain_idx.copy()
+    bad[0, 0] = B + 1
+    rc = lib.va_gdn_plan_tables(ptr(block_addr), None, ptr(bad), ptr(target_idx), None, 0, None, 0, None, 0,
+                                B, L, W, depth, ptr(tab))
+    assert rc == -1   # VA_ERR_BAD_ARG
