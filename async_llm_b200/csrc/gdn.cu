@@ -328,8 +328,9 @@ struct ComposeParams {
 };
 
 // grid (H, W), 256 threads; X (dv x dk), its successor and the level's A_j in shared memory
-// (3 x 64 KB).  Thread (ty, tx) owns the 8x8 block rows 8ty.., cols 8tx.. of X A_j + B_j and sums
-// over i in ascending order.  (With A_j's rows read from global memory inside the loop a level took
+// (3 x 64 KB).  Thread (ty, tx) owns rows 8ty.. and the columns 4tx..4tx+3 and 64+4tx..64+4tx+3
+// of X A_j + B_j (two runs, so that a warp's 16-byte reads of a row of A_j are contiguous: no bank
+// conflict) and sums over i in ascending order.  (With A_j's rows read from global memory inside the loop a level took
 // 146 us for 256 (worker, head) pairs, a tenth of the fp32 rate: every step waited for its row.)
 template <bool kBf16>
 __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant__ ComposeParams p) {
@@ -374,8 +375,8 @@ __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant_
       for (int r = 0; r < 8; ++r) xv[r] = *reinterpret_cast<const float4*>(cur + (ty * 8 + r) * kD + i0);
 #pragma unroll
       for (int ii = 0; ii < 4; ++ii) {
-        const float4 a0 = *reinterpret_cast<const float4*>(as + (i0 + ii) * kD + tx * 8);
-        const float4 a1 = *reinterpret_cast<const float4*>(as + (i0 + ii) * kD + tx * 8 + 4);
+        const float4 a0 = *reinterpret_cast<const float4*>(as + (i0 + ii) * kD + tx * 4);
+        const float4 a1 = *reinterpret_cast<const float4*>(as + (i0 + ii) * kD + kD / 2 + tx * 4);
         const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
@@ -387,13 +388,13 @@ __global__ void __launch_bounds__(256) gdn_compose_kernel(const __grid_constant_
     }
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-      const int64_t brow = head_off + static_cast<int64_t>(ty * 8 + r) * kD + tx * 8;
+      const int64_t brow = head_off + static_cast<int64_t>(ty * 8 + r) * kD + tx * 4;
       const float4 b0 = IO::widen(IO::ld(bj, brow));
-      const float4 b1 = IO::widen(IO::ld(bj, brow + 4));
-      float* dst = nxt + (ty * 8 + r) * kD + tx * 8;
+      const float4 b1 = IO::widen(IO::ld(bj, brow + kD / 2));
+      float* dst = nxt + (ty * 8 + r) * kD + tx * 4;
       *reinterpret_cast<float4*>(dst) =
           make_float4(acc[r][0] + b0.x, acc[r][1] + b0.y, acc[r][2] + b0.z, acc[r][3] + b0.w);
-      *reinterpret_cast<float4*>(dst + 4) =
+      *reinterpret_cast<float4*>(dst + kD / 2) =
           make_float4(acc[r][4] + b1.x, acc[r][5] + b1.y, acc[r][6] + b1.z, acc[r][7] + b1.w);
     }
     __syncthreads();
